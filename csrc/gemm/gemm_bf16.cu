@@ -1,0 +1,316 @@
+// Persistent bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T (+ D), fp32 accumulation in TMEM.
+//
+//  * operands are staged by TMA (128-byte swizzle, non-multicast) through a 4-deep mbarrier ring,
+//  * one elected thread issues tcgen05.mma 128x256x16 into one of two 256-column TMEM accumulators,
+//  * four epilogue warps drain the other accumulator with tcgen05.ld while the next tile computes.
+//
+// Either operand may be "MN-major" (stored transposed, i.e. [K, M] / [K, N] row-major), which is
+// what dgrad (dX = dY * W) and wgrad (dW = dY^T * X) need, so no transposes are ever materialised.
+// Every wait is bounded; on a timeout the kernel records a Status and unwinds through the normal
+// teardown (outstanding copies drained, TMEM freed).
+#include "../common/ptx.cuh"
+#include "../common/tma_host.h"
+#include "gemm.h"
+
+namespace zx {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int CHUNK_BYTES = 64 * BK * 2;    // one 64-wide MN chunk of an MN-major tile: 8 KB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+
+struct KParams {
+  int M, N, K;
+  int ldc, ldd;
+  void* C;
+  const void* D;
+  int out_fp32;
+  int d_mode;  // 0: none, 1: bf16 addend, 2: fp32 addend
+  int num_m, num_n;
+  Status* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm, int& tn) {
+  constexpr int GM = 16;
+  const int per_group = GM * num_n;
+  const int g = t / per_group;
+  const int first_m = g * GM;
+  const int gsize = min(num_m - first_m, GM);
+  const int r = t - g * per_group;
+  tm = first_m + r % gsize;
+  tn = r / gsize;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint64_t* full = bars;                 // [STAGES]
+  uint64_t* empty = bars + STAGES;       // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;      // [2]
+  uint64_t* acc_empty = bars + 2 * STAGES + 2; // [2]
+  uint64_t* drain_bar = bars + 2 * STAGES + 4; // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m * p.num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;  // global k-block counter -> stage / phase
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.num_m, p.num_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tmA, &full[s], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * CHUNK_BYTES, &tmA, &full[s], m0 + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &tmB, &full[s], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * CHUNK_BYTES, &tmB, &full[s], n0 + c * 64, kb * BK);
+          }
+        }
+      }
+      if (!ok) {
+        report(p.status, ZX_ERR_TIMEOUT, /*site=*/1, (int)it);
+        // Loads already issued still land in shared memory: give them a bounded moment to finish.
+        const uint32_t outstanding = it < (uint32_t)STAGES ? it : (uint32_t)STAGES;
+        for (uint32_t j = 0; j < outstanding; ++j) {
+          const uint32_t jt = it - 1 - j;
+          uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full[jt % STAGES], (jt / STAGES) & 1) && globaltimer_ns() - t0 < 50000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0;
+      uint32_t lt = 0;  // local tile counter
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+        const uint32_t buf = lt & 1;
+        if (!mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc_sw128(a_addr + k * UMMA_K * 128, CHUNK_BYTES, 1024)
+                                         : make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_addr + k * UMMA_K * 128, CHUNK_BYTES, 1024)
+                                         : make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
+            umma_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+      if (!ok) {
+        report(p.status, ZX_ERR_TIMEOUT, /*site=*/2, (int)it);
+        umma_commit(drain_bar);
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps -----------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+      int tm, tn;
+      tile_coords(t, p.num_m, p.num_n, tm, tn);
+      const uint32_t buf = lt & 1;
+      if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_addr(tmem_base, q * 32, buf * BN + c * 32), r);
+        tmem_wait_ld();
+        const int col0 = tn * BN + c * 32;
+        if (row_ok && col0 < p.N) {
+          // N is a multiple of 8, so validity is decided per group of 8 columns.
+          if (p.d_mode == 1) {
+            const uint4* dsrc = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.D) +
+                                                               (size_t)row * p.ldd + col0);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 < p.N) {
+                uint4 v = dsrc[g];
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(w[j]);
+                  r[g * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j]) + f.x);
+                  r[g * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j + 1]) + f.y);
+                }
+              }
+            }
+          } else if (p.d_mode == 2) {
+            const float4* dsrc =
+                reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.D) + (size_t)row * p.ldd + col0);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 < p.N) {
+                float4 v = dsrc[g];
+                r[g * 4 + 0] = __float_as_uint(__uint_as_float(r[g * 4 + 0]) + v.x);
+                r[g * 4 + 1] = __float_as_uint(__uint_as_float(r[g * 4 + 1]) + v.y);
+                r[g * 4 + 2] = __float_as_uint(__uint_as_float(r[g * 4 + 2]) + v.z);
+                r[g * 4 + 3] = __float_as_uint(__uint_as_float(r[g * 4 + 3]) + v.w);
+              }
+            }
+          }
+          if (p.out_fp32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 < p.N)
+                dst[g] = make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                                     __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+            }
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 < p.N) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+                dst[g] = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+    if (!ok && lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/3, (int)lt);
+  }
+
+  // ------------------------------- teardown -------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+void launch_variant(const GemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& p, int grid) {
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("gemm: cannot raise shared memory limit: ") + cudaGetErrorString(e));
+    configured = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, a.stream>>>(tmA, tmB, p);
+}
+
+}  // namespace
+
+void launch_gemm_bf16(const GemmArgs& a) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) return;
+  if (a.N % 8 != 0 || a.K % 8 != 0) throw std::runtime_error("gemm_bf16: N and K must be multiples of 8");
+  if (a.a_mn && a.M % 8 != 0) throw std::runtime_error("gemm_bf16: M must be a multiple of 8 for a transposed A");
+  if (a.lda % 8 != 0 || a.ldb % 8 != 0 || a.ldc % (a.out_fp32 ? 4 : 8) != 0)
+    throw std::runtime_error("gemm_bf16: leading dimensions must keep rows 16-byte aligned");
+  if (a.d_mode != 0 && (a.D == nullptr || a.ldd % (a.d_mode == 2 ? 4 : 8) != 0))
+    throw std::runtime_error("gemm_bf16: bad addend");
+
+  // K-major operand: global [rows, K]; box 64 (K) x rows-per-tile.
+  // MN-major operand: global [K, rows]; box 64 (rows) x 64 (K), several boxes per stage.
+  CUtensorMap tmA = a.a_mn ? make_tma_2d(a.A, 2, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.lda, 64, BK)
+                           : make_tma_2d(a.A, 2, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
+  CUtensorMap tmB = a.b_mn ? make_tma_2d(a.B, 2, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.ldb, 64, BK)
+                           : make_tma_2d(a.B, 2, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN);
+  KParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.ldc = a.ldc; p.ldd = a.ldd;
+  p.C = a.C; p.D = a.D;
+  p.out_fp32 = a.out_fp32; p.d_mode = a.d_mode;
+  p.num_m = (a.M + BM - 1) / BM;
+  p.num_n = (a.N + BN - 1) / BN;
+  p.status = a.status;
+  const int tiles = p.num_m * p.num_n;
+  const int grid = tiles < a.sm_count ? tiles : a.sm_count;
+  if (a.a_mn) {
+    if (a.b_mn) launch_variant<true, true>(a, tmA, tmB, p, grid);
+    else launch_variant<true, false>(a, tmA, tmB, p, grid);
+  } else {
+    if (a.b_mn) launch_variant<false, true>(a, tmA, tmB, p, grid);
+    else launch_variant<false, false>(a, tmA, tmB, p, grid);
+  }
+}
+
+}  // namespace zx

@@ -1,0 +1,323 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from zenyx_b200.ops import _ext
+
+    return _ext.C()
+
+
+def _status_ok():
+    from zenyx_b200.ops import _ext
+
+    _ext.check_status()
+
+
+def _rel_err(a, b):
+    a = a.float()
+    b = b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 264, 136), (1000, 768, 520)])
+def test_gemm_layouts(C, a_t, b_t, M, N, K):
+    torch.manual_seed(0)
+    dev = "cuda"
+    if a_t and M % 8:
+        pytest.skip("transposed A needs M % 8 == 0")
+    a = torch.randn(M, K, device=dev).bfloat16()
+    b = torch.randn(N, K, device=dev).bfloat16()
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_t else a
+    b_in = b.t().contiguous() if b_t else b
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    C.gemm(a_in, b_in, out, a_t, b_t, None)
+    _status_ok()
+    assert _rel_err(out, ref) < 1e-2
+    # fp32 output with an fp32 addend aliasing the output (gradient accumulation)
+    acc = torch.randn(M, N, device=dev, dtype=torch.float32)
+    ref2 = acc + ref
+    C.gemm(a_in, b_in, acc, a_t, b_t, acc)
+    _status_ok()
+    assert _rel_err(acc, ref2) < 1e-3
+    # bf16 output with a bf16 addend (residual connection)
+    res = torch.randn(M, N, device=dev).bfloat16()
+    out3 = torch.empty_like(res)
+    C.gemm(a_in, b_in, out3, a_t, b_t, res)
+    _status_ok()
+    assert _rel_err(out3, ref + res.float()) < 1e-2
+
+
+def test_gemm_large_persistent(C):
+    torch.manual_seed(1)
+    M, N, K = 4096, 4096, 1024
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    C.gemm(a, b, out, False, False, None)
+    _status_ok()
+    ref = a.float() @ b.float().t()
+    assert _rel_err(out, ref) < 1e-2
+
+
+def _attn_ref(q, k, v, scale, qpos, kpos, causal, window_blocks=0, global_every=0):
+    """q [B,Sq,Hq,D], k/v [B,Skv,Hkv,D]; qpos/kpos global token positions. fp32 math."""
+    B, Sq, Hq, D = q.shape
+    Hkv = k.shape[2]
+    g = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", qf, kf) * scale
+    mask = torch.ones(Sq, k.shape[1], dtype=torch.bool, device=q.device)
+    if causal:
+        mask &= kpos[None, :] <= qpos[:, None]
+    if window_blocks > 0:
+        qb = (qpos // 128)[:, None]
+        kb = (kpos // 128)[None, :]
+        keep = (qb - kb).abs() < window_blocks
+        if global_every > 0:
+            keep |= (kb % global_every) == 0
+        mask &= keep
+    s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    p = torch.nan_to_num(p, nan=0.0)
+    o = torch.einsum("bhqk,bhkd->bhqd", p, vf).permute(0, 2, 1, 3)
+    return o, lse
+
+
+def _positions(chunk_pos, S):
+    n = len(chunk_pos)
+    L = S // n
+    return torch.cat([torch.arange(p, p + L) for p in chunk_pos]).cuda()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 256, 4, 1), (2, 512, 8, 2), (1, 384, 4, 4)])
+def test_attn_fwd_basic(C, causal, B, S, Hq, Hkv):
+    torch.manual_seed(2)
+    D = 128
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False)
+    _status_ok()
+    pos = torch.arange(S, device="cuda")
+    o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, causal)
+    assert _rel_err(o, o_ref) < 2e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+
+
+def test_attn_fwd_strided_qkv_and_long(C):
+    """Q/K/V as column blocks of one fused projection buffer; enough KV tiles to cycle the ring."""
+    torch.manual_seed(3)
+    B, S, Hq, Hkv, D = 1, 2048, 4, 2, 128
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    q = qkv[:, : Hq * D].view(B, S, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hkv) * D].view(B, S, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D :].view(B, S, Hkv, D)
+    o = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 0, 0, [0], [0], False)
+    _status_ok()
+    pos = torch.arange(S, device="cuda")
+    o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, True)
+    assert _rel_err(o, o_ref) < 2e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+
+
+def test_attn_fwd_zigzag_ring_merge(C):
+    """Emulates a 2-rank zigzag ring on one GPU: rank 0 holds chunks (0, 3), rank 1 holds (1, 2).
+    Two calls (own KV, then the peer's KV with merge_prev) must equal full causal attention."""
+    torch.manual_seed(4)
+    B, S, Hq, Hkv, D = 1, 1024, 4, 2, 128
+    L = S // 4
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(D)
+    pos = torch.arange(S, device="cuda")
+    o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, True)
+    chunks = {0: [0, 3], 1: [1, 2]}
+
+    def shard(t, r):
+        return torch.cat([t[:, c * L : (c + 1) * L] for c in chunks[r]], dim=1).contiguous()
+
+    for r in (0, 1):
+        qr = shard(q, r)
+        o = torch.empty_like(qr)
+        lse = torch.empty(B, Hq, 2 * L, device="cuda", dtype=torch.float32)
+        qpos = [c * L for c in chunks[r]]
+        for step, owner in enumerate([r, 1 - r]):
+            C.attn_fwd(qr, shard(k, owner), shard(v, owner), o, lse, scale, True, 0, 0, qpos,
+                       [c * L for c in chunks[owner]], step > 0)
+        _status_ok()
+        o_exp = shard(o_ref, r)
+        lse_exp = torch.cat([lse_ref[:, :, c * L : (c + 1) * L] for c in chunks[r]], dim=2)
+        assert _rel_err(o, o_exp) < 2e-2
+        assert (lse - lse_exp).abs().max().item() < 2e-2
+
+
+def test_attn_fwd_block_sparse(C):
+    torch.manual_seed(5)
+    B, S, Hq, Hkv, D = 1, 2048, 2, 1, 128
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 3, 4, [0], [0], False)
+    _status_ok()
+    pos = torch.arange(S, device="cuda")
+    o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, True, 3, 4)
+    assert _rel_err(o, o_ref) < 2e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+
+
+def test_rmsnorm(C):
+    torch.manual_seed(6)
+    rows, H = 777, 4096
+    x = torch.randn(rows, H, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, device="cuda")
+    C.rmsnorm_fwd(x, w, y, rstd, 1e-5)
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    assert _rel_err(y, ref) < 1e-2
+    dy = torch.randn_like(x)
+    ref.backward(dy.float())
+    dx = torch.empty_like(x)
+    dw = torch.zeros(H, device="cuda")
+    C.rmsnorm_bwd(dy, x, w, rstd, dx, dw)
+    assert _rel_err(dx, xf.grad) < 1e-2
+    assert _rel_err(dw, wf.grad) < 1e-2
+
+
+def test_swiglu(C):
+    torch.manual_seed(7)
+    T, F = 300, 1024
+    gu = torch.randn(T, 2 * F, device="cuda").bfloat16()
+    h = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+    C.swiglu_fwd(gu, h)
+    guf = gu.float().requires_grad_(True)
+    ref = torch.nn.functional.silu(guf[:, :F]) * guf[:, F:]
+    assert _rel_err(h, ref) < 1e-2
+    dh = torch.randn_like(h)
+    ref.backward(dh.float())
+    dgu = torch.empty_like(gu)
+    C.swiglu_bwd(gu, dh, dgu)
+    assert _rel_err(dgu, guf.grad) < 1e-2
+
+
+def test_rope(C):
+    torch.manual_seed(8)
+    T, Hq, Hkv, D = 256, 4, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    pos = torch.arange(T, device="cuda").float() * 3 + 5
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+
+    def rot(x):  # x [T, H, D]
+        x1, x2 = x[..., : D // 2], x[..., D // 2 :]
+        return torch.cat([x1 * cos[:, None] - x2 * sin[:, None], x2 * cos[:, None] + x1 * sin[:, None]], -1)
+
+    qf = qkv[:, : Hq * D].float().view(T, Hq, D)
+    kf = qkv[:, Hq * D : (Hq + Hkv) * D].float().view(T, Hkv, D)
+    vf = qkv[:, (Hq + Hkv) * D :].float().view(T, Hkv, D).clone()
+    work = qkv.clone()
+    k_out = torch.empty(T, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    v_out = torch.empty(T, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    C.rope_qkv(work, cos, sin, k_out, v_out, Hq, Hkv, D, T, False)
+    assert _rel_err(work[:, : Hq * D].view(T, Hq, D), rot(qf)) < 1e-2
+    assert _rel_err(k_out, rot(kf)) < 1e-2
+    assert torch.equal(v_out.float(), vf)
+    # in place + inverse restores the input up to bf16 rounding
+    work2 = qkv.clone()
+    C.rope_qkv(work2, cos, sin, None, None, Hq, Hkv, D, T, False)
+    C.rope_qkv(work2, cos, sin, None, None, Hq, Hkv, D, T, True)
+    assert _rel_err(work2, qkv) < 1e-2
+
+
+def test_embedding_and_ce(C):
+    torch.manual_seed(9)
+    V, H, T = 1024, 256, 500
+    table = torch.randn(V, H, device="cuda").bfloat16()
+    ids = torch.randint(0, V, (T,), device="cuda")
+    out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    C.embedding_fwd(ids, table, out)
+    assert torch.equal(out, table[ids])
+    dout = torch.randn(T, H, device="cuda").bfloat16()
+    dtab = torch.zeros(V, H, device="cuda")
+    C.embedding_bwd(ids, dout, dtab)
+    ref = torch.zeros(V, H, device="cuda").index_add_(0, ids, dout.float())
+    assert _rel_err(dtab, ref) < 1e-5
+
+    logits = (3 * torch.randn(T, V, device="cuda")).bfloat16()
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    lf = logits.float().requires_grad_(True)
+    loss_ref = torch.nn.functional.cross_entropy(lf, tgt, reduction="none")
+    loss_ref.sum().backward()
+    work = logits.clone()
+    loss = torch.empty(T, device="cuda")
+    C.ce_fwd_bwd(work, tgt, loss, 0.5, -100)
+    assert (loss - loss_ref).abs().max().item() < 2e-2
+    assert _rel_err(work, 0.5 * lf.grad) < 2e-2
+
+
+def test_kv_quant(C):
+    torch.manual_seed(10)
+    T, Hkv, D = 512, 2, 128
+    x = (torch.randn(T, Hkv, D, device="cuda") * torch.rand(1, Hkv, 1, device="cuda") * 4).bfloat16()
+    q = torch.empty(T, Hkv, D, device="cuda", dtype=torch.uint8)
+    scales = torch.empty(T // 128, Hkv, device="cuda")
+    C.kv_quant_e4m3(x, q, scales, None, 128)
+    amax = x.float().view(T // 128, 128, Hkv, D).abs().amax(dim=(1, 3))
+    assert torch.allclose(scales, amax / 448.0, rtol=1e-6)
+    ref_q = (x.float().view(T // 128, 128, Hkv, D) / scales[:, None, :, None]).view(T, Hkv, D).to(torch.float8_e4m3fn)
+    mismatch = (q.view(torch.float8_e4m3fn).float() != ref_q.float()).float().mean().item()
+    assert mismatch < 1e-3
+    back = torch.empty_like(x)
+    C.kv_dequant_e4m3(q, scales, back, 128)
+    assert _rel_err(back, x) < 0.05
+
+
+def test_adamw_split_master(C):
+    torch.manual_seed(11)
+    n = 4096 * 3
+    w0 = torch.randn(n, device="cuda")
+    p = torch.nn.Parameter(w0.clone())
+    opt = torch.optim.AdamW([p], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    bits = w0.view(torch.int32)
+    hi = ((bits + 0x8000) >> 16).to(torch.int16)
+    lo = (bits - (hi.to(torch.int32) << 16)).to(torch.int16)
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    for step in range(1, 4):
+        g = torch.randn(n, device="cuda")
+        p.grad = g.clone()
+        opt.step()
+        C.adamw(hi, lo, m, v, g, 3e-4, 0.9, 0.95, 1e-8, 0.1, step, 1.0, None)
+    master = ((hi.to(torch.int32) << 16) + lo.to(torch.int32)).view(torch.float32)
+    assert (master - p.data).abs().max().item() < 1e-6
+    # the bf16 half is the nearest-bf16 of the master (ties up)
+    assert _rel_err(hi.view(torch.bfloat16), master) < 4e-3
+    ss = torch.zeros(1, device="cuda")
+    C.sumsq(g, ss)
+    assert abs(ss.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
