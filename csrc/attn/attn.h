@@ -54,15 +54,16 @@ struct AttnBwdArgs {
   const void* d_o = nullptr;  // [B, Sq, Hq, 128]
   const float* lse = nullptr; // [B, Hq, Sq]
   float* delta = nullptr;     // [B, Hq, Sq] scratch: rowsum(dO * O), written by the pre-pass
-  float* dq = nullptr;        // [B, Sq, Hq, 128] fp32, accumulated with red.add (caller zeroes)
-  float* dk = nullptr;        // [B, Skv, Hkv, 128] fp32, accumulated (may be a peer's buffer)
-  float* dv = nullptr;        // [B, Skv, Hkv, 128] fp32, accumulated (may be a peer's buffer)
+  float* dq = nullptr;        // [B, Sq, Hq, 128] fp32, written (or accumulated when dq_accumulate)
+  float* dk = nullptr;        // [B, Skv, Hkv, 128] fp32, red.add target, caller zeroes (may be a peer's buffer)
+  float* dv = nullptr;        // [B, Skv, Hkv, 128] fp32, red.add target, caller zeroes (may be a peer's buffer)
   int B = 1, Hq = 0, Hkv = 0, Sq = 0, Skv = 0;
   int64_t q_tok_stride = 0, k_tok_stride = 0, v_tok_stride = 0;
   float scale = 0.f;
   AttnMask mask;
   AttnLayout q_layout, kv_layout;
   int compute_delta = 1;  // run the delta pre-pass (once per backward; later ring steps reuse it)
+  int dq_accumulate = 0;  // add to the dq already present instead of overwriting it (ring step > 0)
   Status* status = nullptr;
   cudaStream_t stream = nullptr;
 };

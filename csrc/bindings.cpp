@@ -152,7 +152,7 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
               Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, int64_t window_blocks,
               int64_t global_every, const std::vector<int64_t>& q_chunk_pos, const std::vector<int64_t>& kv_chunk_pos,
-              bool compute_delta) {
+              bool compute_delta, bool dq_accumulate) {
   check_qkv(q, "q");
   check_qkv(k, "k");
   check_qkv(v, "v");
@@ -177,6 +177,7 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.q_layout = to_layout(q_chunk_pos, a.Sq);
   a.kv_layout = to_layout(kv_chunk_pos, a.Skv);
   a.compute_delta = compute_delta;
+  a.dq_accumulate = dq_accumulate;
   a.status = status_ptr();
   a.stream = cur_stream();
   zx::launch_attn_bwd(a);

@@ -250,7 +250,7 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int6
   const int row = blockIdx.x;
   __nv_bfloat16* lr = logits + (size_t)row * ld;
   const int nvec = V >> 3;
-  float m = -INFINITY, l = 0.f;
+  float m = -1.0e30f, l = 0.f;  // finite sentinel: idle threads must not produce inf - inf
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     float f[8];
     unpack8(reinterpret_cast<const uint4*>(lr)[i], f);
@@ -270,7 +270,7 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int6
   float wl = warp_sum(l * __expf(m - wm));
   if (lane == 0) { s_m[warp] = wm; s_l[warp] = wl; }
   __syncthreads();
-  float bm = lane < nwarps ? s_m[lane] : -INFINITY;
+  float bm = lane < nwarps ? s_m[lane] : -1.0e30f;
   float bl = lane < nwarps ? s_l[lane] : 0.f;
   const float gm = warp_max(bm);
   const float gl = warp_sum(bl * __expf(bm - gm));

@@ -321,3 +321,103 @@ def test_adamw_split_master(C):
     ss = torch.zeros(1, device="cuda")
     C.sumsq(g, ss)
     assert abs(ss.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
+
+
+def _attn_bwd_ref(q, k, v, do, scale, qpos, kpos, causal, wb=0, ge=0):
+    qf = q.float().requires_grad_(True)
+    kf = k.float().requires_grad_(True)
+    vf = v.float().requires_grad_(True)
+    o, _ = _attn_ref(qf, kf, vf, scale, qpos, kpos, causal, wb, ge)
+    o.backward(do.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 256, 4, 1), (2, 512, 4, 2), (1, 1024, 2, 2)])
+def test_attn_bwd_basic(C, causal, B, S, Hq, Hkv):
+    torch.manual_seed(12)
+    D = 128
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False)
+    delta = torch.empty_like(lse)
+    dq = torch.empty(B, S, Hq, D, device="cuda")
+    dk = torch.zeros(B, S, Hkv, D, device="cuda")
+    dv = torch.zeros(B, S, Hkv, D, device="cuda")
+    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, causal, 0, 0, [0], [0], True, False)
+    _status_ok()
+    pos = torch.arange(S, device="cuda")
+    dq_r, dk_r, dv_r = _attn_bwd_ref(q, k, v, do, scale, pos, pos, causal)
+    assert _rel_err(dv, dv_r) < 2e-2
+    assert _rel_err(dk, dk_r) < 2e-2
+    assert _rel_err(dq, dq_r) < 2e-2
+
+
+def test_attn_bwd_zigzag_ring(C):
+    """Two emulated zigzag ranks: each rank's backward runs one call per KV owner, accumulating dQ
+    locally and adding dK/dV into the owner's buffers, exactly like the ring does over peer memory."""
+    torch.manual_seed(13)
+    B, S, Hq, Hkv, D = 1, 1024, 4, 2, 128
+    L = S // 4
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(D)
+    pos = torch.arange(S, device="cuda")
+    dq_r, dk_r, dv_r = _attn_bwd_ref(q, k, v, do, scale, pos, pos, True)
+    chunks = {0: [0, 3], 1: [1, 2]}
+
+    def shard(t, r):
+        return torch.cat([t[:, c * L : (c + 1) * L] for c in chunks[r]], dim=1).contiguous()
+
+    dk_own = {r: torch.zeros(B, 2 * L, Hkv, D, device="cuda") for r in (0, 1)}
+    dv_own = {r: torch.zeros(B, 2 * L, Hkv, D, device="cuda") for r in (0, 1)}
+    for r in (0, 1):
+        qr, dor = shard(q, r), shard(do, r)
+        o = torch.empty_like(qr)
+        lse = torch.empty(B, Hq, 2 * L, device="cuda", dtype=torch.float32)
+        qpos = [c * L for c in chunks[r]]
+        order = [r, 1 - r]
+        for step, owner in enumerate(order):
+            C.attn_fwd(qr, shard(k, owner), shard(v, owner), o, lse, scale, True, 0, 0, qpos,
+                       [c * L for c in chunks[owner]], step > 0)
+        delta = torch.empty_like(lse)
+        dq = torch.empty(B, 2 * L, Hq, D, device="cuda")
+        for step, owner in enumerate(order):
+            C.attn_bwd(qr, shard(k, owner), shard(v, owner), o, dor, lse, delta, dq, dk_own[owner], dv_own[owner],
+                       scale, True, 0, 0, qpos, [c * L for c in chunks[owner]], step == 0, step > 0)
+        _status_ok()
+        assert _rel_err(dq, shard(dq_r, r)) < 2e-2
+    for r in (0, 1):
+        assert _rel_err(dk_own[r], shard(dk_r, r)) < 2e-2
+        assert _rel_err(dv_own[r], shard(dv_r, r)) < 2e-2
+
+
+def test_attn_bwd_block_sparse(C):
+    torch.manual_seed(14)
+    B, S, Hq, Hkv, D = 1, 1536, 2, 1, 128
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 2, 4, [0], [0], False)
+    delta = torch.empty_like(lse)
+    dq = torch.empty(B, S, Hq, D, device="cuda")
+    dk = torch.zeros(B, S, Hkv, D, device="cuda")
+    dv = torch.zeros(B, S, Hkv, D, device="cuda")
+    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, True, 2, 4, [0], [0], True, False)
+    _status_ok()
+    pos = torch.arange(S, device="cuda")
+    dq_r, dk_r, dv_r = _attn_bwd_ref(q, k, v, do, scale, pos, pos, True, 2, 4)
+    assert _rel_err(dv, dv_r) < 2e-2
+    assert _rel_err(dk, dk_r) < 2e-2
+    assert _rel_err(dq, dq_r) < 2e-2
