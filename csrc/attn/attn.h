@@ -8,6 +8,7 @@
 // so a masked-out 128x128 tile is never loaded or multiplied.
 #pragma once
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 #include "../common/status.h"
 
@@ -40,6 +41,12 @@ struct AttnFwdArgs {
   AttnMask mask;
   AttnLayout q_layout, kv_layout;
   int merge_prev = 0;  // fold the result into the o/lse already present (ring step > 0)
+  // Optional transfer fused into the kernel: one extra warp per CTA copies its slice of
+  // [pull_src, pull_src + pull_bytes) (typically the next ring step's K/V in a peer GPU's memory)
+  // into pull_dst (local staging) with plain P2P loads while the CTA computes.
+  const void* pull_src = nullptr;
+  void* pull_dst = nullptr;
+  size_t pull_bytes = 0;
   Status* status = nullptr;
   cudaStream_t stream = nullptr;
 };
@@ -64,6 +71,9 @@ struct AttnBwdArgs {
   AttnLayout q_layout, kv_layout;
   int compute_delta = 1;  // run the delta pre-pass (once per backward; later ring steps reuse it)
   int dq_accumulate = 0;  // add to the dq already present instead of overwriting it (ring step > 0)
+  const void* pull_src = nullptr;  // same fused peer pull as in the forward (done by the dK/dV kernel)
+  void* pull_dst = nullptr;
+  size_t pull_bytes = 0;
   Status* status = nullptr;
   cudaStream_t stream = nullptr;
 };

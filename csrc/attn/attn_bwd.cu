@@ -28,6 +28,7 @@ constexpr int BT = 128;                    // tile edge in tokens (both Q and KV
 constexpr int TILE_BYTES = BT * HD * 2;    // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk
 constexpr int NUM_THREADS = 192;           // 4 compute warps + TMA warp + MMA warp
+constexpr int DKDV_THREADS = 224;          // ... + peer-pull warp
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -45,6 +46,9 @@ struct BwdParams {
   float* dk;
   float* dv;
   int dq_accumulate;
+  const uint4* pull_src;
+  uint4* pull_dst;
+  size_t pull_nvec;
   Status* status;
 };
 
@@ -122,7 +126,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 constexpr int DKDV_SMEM = 2 * TILE_BYTES /*K,V*/ + 4 * TILE_BYTES /*Q,dO x2*/ + 3 * 2 * BT * 4 /*lse,delta,lse2*/ +
                           1024 + 256;
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(DKDV_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -187,7 +191,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (tile_allowed(p, q_tile_pos(p, t), kpos0)) ++n_items;
   n_items *= G;
 
-  if (n_items > 0) {
+  if (warp == 6) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
+
+  if (n_items > 0 && warp < 6) {
     if (warp == 4) {
       // ------------------------------- TMA producer -------------------------------
       if (lane == 0) {
@@ -670,6 +676,10 @@ void launch_attn_bwd(const AttnBwdArgs& a) {
   p.lse = a.lse; p.delta = a.delta;
   p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
   p.dq_accumulate = a.dq_accumulate;
+  if (a.pull_bytes % 16 != 0) throw std::runtime_error("attn_bwd: pull size must be a multiple of 16 bytes");
+  p.pull_src = (const uint4*)a.pull_src;
+  p.pull_dst = (uint4*)a.pull_dst;
+  p.pull_nvec = a.pull_src != nullptr ? a.pull_bytes / 16 : 0;
   p.status = a.status;
   static bool configured = false;
   if (!configured) {
@@ -677,7 +687,7 @@ void launch_attn_bwd(const AttnBwdArgs& a) {
     set_smem(attn_bwd_dq_kernel, DQ_SMEM, "attn_bwd_dq");
     configured = true;
   }
-  attn_bwd_dkdv_kernel<<<p.n_kv_tiles * a.B * a.Hkv, NUM_THREADS, DKDV_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
+  attn_bwd_dkdv_kernel<<<p.n_kv_tiles * a.B * a.Hkv, DKDV_THREADS, DKDV_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
   attn_bwd_dq_kernel<<<p.n_q_tiles * a.B * a.Hq, NUM_THREADS, DQ_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
 }
 

@@ -3,6 +3,8 @@
 // One CTA owns two adjacent 128-row Q tiles of one head and walks the KV buffer once:
 //   warp 8      TMA producer: Q once, then K/V tiles through a 2-stage ring (non-multicast loads)
 //   warp 9      MMA issuer:   S_i = Q_i K^T  (SS form) and O_i += P_i V (A = P read from TMEM)
+//   warp 10     optional peer pull: copies this CTA's slice of the next ring step's K/V from the
+//               owning GPU into local staging with plain P2P loads while the tiles compute
 //   warps 0-3   softmax of Q tile 0, one thread per row, S/P/O live in TMEM
 //   warps 4-7   softmax of Q tile 1
 // The two softmax groups ping-pong so the tensor core always has the other tile's MMAs to run.
@@ -25,7 +27,7 @@ constexpr int BKV = 128;
 constexpr int TILE_BYTES = BQ * HD * 2;   // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk: 128 rows x 128 B
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 352;  // 8 softmax warps + TMA + MMA + peer-pull warp
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256;
 constexpr float NEG_BIG = -1.0e30f;
@@ -42,6 +44,9 @@ struct FwdParams {
   __nv_bfloat16* O;
   float* LSE;
   int merge_prev;
+  const uint4* pull_src;
+  uint4* pull_dst;
+  size_t pull_nvec;
   Status* status;
 };
 
@@ -247,6 +252,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
+  } else if (warp == 10) {
+    // ------------------------------- peer pull ----------------------------------
+    warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
   } else {
     // ------------------------------- softmax groups -----------------------------
     const int i = warp >> 2;       // which Q tile
@@ -444,6 +452,10 @@ void launch_attn_fwd(const AttnFwdArgs& a) {
   p.O = (__nv_bfloat16*)a.o;
   p.LSE = a.lse;
   p.merge_prev = a.merge_prev;
+  if (a.pull_bytes % 16 != 0) throw std::runtime_error("attn_fwd: pull size must be a multiple of 16 bytes");
+  p.pull_src = (const uint4*)a.pull_src;
+  p.pull_dst = (uint4*)a.pull_dst;
+  p.pull_nvec = a.pull_src != nullptr ? a.pull_bytes / 16 : 0;
   p.status = a.status;
   static bool configured = false;
   if (!configured) {

@@ -8,6 +8,8 @@
 #include "common/status.h"
 #include "fused/fused_ops.h"
 #include "gemm/gemm.h"
+#include "optim/zero.h"
+#include "peer/peer.h"
 
 namespace {
 
@@ -121,7 +123,8 @@ void check_qkv(const Tensor& t, const char* name) {
 // q [B,Sq,Hq,128], k/v [B,Skv,Hkv,128] (token-strided views are fine); o [B,Sq,Hq,128], lse [B,Hq,Sq].
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, double scale, bool causal,
               int64_t window_blocks, int64_t global_every, const std::vector<int64_t>& q_chunk_pos,
-              const std::vector<int64_t>& kv_chunk_pos, bool merge_prev) {
+              const std::vector<int64_t>& kv_chunk_pos, bool merge_prev, int64_t pull_src, int64_t pull_dst,
+              int64_t pull_bytes) {
   check_qkv(q, "q");
   check_qkv(k, "k");
   check_qkv(v, "v");
@@ -143,6 +146,9 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
   a.q_layout = to_layout(q_chunk_pos, a.Sq);
   a.kv_layout = to_layout(kv_chunk_pos, a.Skv);
   a.merge_prev = merge_prev;
+  a.pull_src = reinterpret_cast<const void*>(pull_src);
+  a.pull_dst = reinterpret_cast<void*>(pull_dst);
+  a.pull_bytes = (size_t)pull_bytes;
   a.status = status_ptr();
   a.stream = cur_stream();
   zx::launch_attn_fwd(a);
@@ -152,7 +158,7 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
               Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, int64_t window_blocks,
               int64_t global_every, const std::vector<int64_t>& q_chunk_pos, const std::vector<int64_t>& kv_chunk_pos,
-              bool compute_delta, bool dq_accumulate) {
+              bool compute_delta, bool dq_accumulate, int64_t pull_src, int64_t pull_dst, int64_t pull_bytes) {
   check_qkv(q, "q");
   check_qkv(k, "k");
   check_qkv(v, "v");
@@ -178,6 +184,9 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.kv_layout = to_layout(kv_chunk_pos, a.Skv);
   a.compute_delta = compute_delta;
   a.dq_accumulate = dq_accumulate;
+  a.pull_src = reinterpret_cast<const void*>(pull_src);
+  a.pull_dst = reinterpret_cast<void*>(pull_dst);
+  a.pull_bytes = (size_t)pull_bytes;
   a.status = status_ptr();
   a.stream = cur_stream();
   zx::launch_attn_bwd(a);
@@ -197,7 +206,8 @@ void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor& y, Tensor& rstd, doub
   check_launch("rmsnorm_fwd");
 }
 
-void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& dx, Tensor& dw_accum) {
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& dx, Tensor& dw_accum,
+                 const c10::optional<Tensor>& dres) {
   check_bf16(dy, "dy"); check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(dx, "dx");
   TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous(), "rmsnorm_bwd: contiguous expected");
   const int H = (int)x.size(-1);
@@ -206,7 +216,13 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
               "dw_accum must be fp32 [H]");
   TORCH_CHECK((size_t)H * 4 <= 48 * 1024, "rmsnorm_bwd: hidden size too large for the shared accumulator");
   c10::cuda::CUDAGuard guard(x.device());
-  zx::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+  const void* dres_p = nullptr;
+  if (dres.has_value()) {
+    check_bf16(*dres, "dres");
+    TORCH_CHECK(dres->is_contiguous() && dres->numel() == x.numel(), "dres must match x");
+    dres_p = dres->data_ptr();
+  }
+  zx::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dres_p, dx.data_ptr(),
                          dw_accum.data_ptr<float>(), rows, H, sm_count(), cur_stream());
   check_launch("rmsnorm_bwd");
 }
@@ -238,6 +254,23 @@ void rope_qkv(Tensor& qkv, const Tensor& cos_t, const Tensor& sin_t, const c10::
   zx::launch_rope_qkv(qkv.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), kp, vp, (int)qkv.size(0),
                       (int)tokens_per_seq, (int)Hq, (int)Hkv, (int)D, inverse ? -1.f : 1.f, sm_count(), cur_stream());
   check_launch("rope_qkv");
+}
+
+// fp32 dq [T,Hq,D], dk/dv [T,Hkv,D] -> bf16 dqkv [T,(Hq+2Hkv)*D] with the inverse rotation on dq, dk
+void rope_bwd_pack(const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& cos_t, const Tensor& sin_t,
+                   Tensor& dqkv, int64_t Hq, int64_t Hkv, int64_t D, int64_t tokens_per_seq) {
+  check_bf16(dqkv, "dqkv");
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&dq, &dk, &dv, &cos_t, &sin_t})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->is_contiguous(), "fp32 contiguous expected");
+  const int64_t T = dqkv.size(0);
+  TORCH_CHECK(dqkv.is_contiguous() && dqkv.size(1) == (Hq + 2 * Hkv) * D && D % 16 == 0, "dqkv shape");
+  TORCH_CHECK(dq.numel() == T * Hq * D && dk.numel() == T * Hkv * D && dv.numel() == T * Hkv * D, "gradient sizes");
+  TORCH_CHECK(cos_t.size(0) >= tokens_per_seq && cos_t.size(1) == D / 2, "rope tables");
+  c10::cuda::CUDAGuard guard(dqkv.device());
+  zx::launch_rope_bwd_pack(dq.data_ptr<float>(), dk.data_ptr<float>(), dv.data_ptr<float>(), cos_t.data_ptr<float>(),
+                           sin_t.data_ptr<float>(), dqkv.data_ptr(), (int)T, (int)tokens_per_seq, (int)Hq, (int)Hkv,
+                           (int)D, sm_count(), cur_stream());
+  check_launch("rope_bwd_pack");
 }
 
 void swiglu_fwd(const Tensor& gu, Tensor& h) {
@@ -355,6 +388,83 @@ void clip_coef(const Tensor& ss, double scale, double max_norm, Tensor& coef, Te
   check_launch("clip_coef");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Peer memory and the fused optimizer
+// ---------------------------------------------------------------------------------------------
+int64_t peer_alloc(int64_t bytes) { return reinterpret_cast<int64_t>(zx::peer_alloc((size_t)bytes)); }
+py::bytes peer_export(int64_t ptr) { return py::bytes(zx::peer_export(reinterpret_cast<void*>(ptr))); }
+int64_t peer_open(const std::string& handle) { return reinterpret_cast<int64_t>(zx::peer_open(handle)); }
+void peer_close(int64_t ptr) { zx::peer_close(reinterpret_cast<void*>(ptr)); }
+void peer_free(int64_t ptr) { zx::peer_free(reinterpret_cast<void*>(ptr)); }
+
+// A tensor view over raw device memory (own or peer-mapped). The caller keeps the memory alive.
+Tensor tensor_from_ptr(int64_t ptr, const std::vector<int64_t>& sizes, torch::ScalarType dtype) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, dev);
+  return torch::from_blob(reinterpret_cast<void*>(ptr), sizes, [](void*) {}, opts);
+}
+
+zx::PeerPtrs to_ptrs(const std::vector<int64_t>& v) {
+  TORCH_CHECK(!v.empty() && (int)v.size() <= zx::kMaxPeers, "between 1 and 8 peers are supported");
+  zx::PeerPtrs p;
+  for (int i = 0; i < zx::kMaxPeers; ++i) p.p[i] = i < (int)v.size() ? reinterpret_cast<void*>(v[i]) : nullptr;
+  return p;
+}
+
+void peer_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, double timeout_ms) {
+  zx::launch_peer_barrier(to_ptrs(flag_ptrs), (int)rank, (int)flag_ptrs.size(), (uint32_t)epoch,
+                          (uint64_t)(timeout_ms * 1e6), status_ptr(), cur_stream());
+  check_launch("peer_barrier");
+}
+
+void peer_pull(int64_t src_ptr, int64_t dst_ptr, int64_t bytes, int64_t blocks) {
+  TORCH_CHECK(bytes % 16 == 0, "peer_pull: size must be a multiple of 16 bytes");
+  zx::launch_peer_pull(reinterpret_cast<const void*>(src_ptr), reinterpret_cast<void*>(dst_ptr), (size_t)bytes,
+                       (int)blocks, cur_stream());
+  check_launch("peer_pull");
+}
+
+void zero_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, int64_t rank,
+               int64_t shard_begin, int64_t n_shard, int64_t decay_end, const c10::optional<Tensor>& g_shard,
+               Tensor& p_lo, Tensor& m, Tensor& v, const c10::optional<Tensor>& sumsq,
+               const c10::optional<Tensor>& clip_coef, bool do_reduce, bool do_update, bool zero_grads,
+               double grad_scale, double lr, double beta1, double beta2, double eps, double weight_decay,
+               int64_t step) {
+  TORCH_CHECK(grad_ptrs.size() == param_ptrs.size(), "zero_step: peer lists differ");
+  TORCH_CHECK(shard_begin % 4 == 0 && n_shard % 4 == 0, "zero_step: shard bounds must be multiples of 4");
+  TORCH_CHECK(p_lo.is_cuda() && p_lo.element_size() == 2 && p_lo.numel() >= n_shard && m.numel() >= n_shard &&
+                  v.numel() >= n_shard && m.scalar_type() == torch::kFloat32 && v.scalar_type() == torch::kFloat32,
+              "zero_step: shard state has the wrong size or type");
+  zx::ZeroArgs a;
+  a.grads = to_ptrs(grad_ptrs);
+  a.params = to_ptrs(param_ptrs);
+  a.nranks = (int)grad_ptrs.size();
+  a.rank = (int)rank;
+  a.shard_begin = (size_t)shard_begin;
+  a.n_shard = (size_t)n_shard;
+  a.decay_end = (size_t)decay_end;
+  if (g_shard.has_value()) {
+    TORCH_CHECK(g_shard->scalar_type() == torch::kFloat32 && g_shard->numel() >= n_shard, "zero_step: g_shard");
+    a.g_shard = g_shard->data_ptr<float>();
+  } else {
+    TORCH_CHECK(do_reduce && do_update, "zero_step: split passes need a g_shard buffer");
+  }
+  a.p_lo = reinterpret_cast<int16_t*>(p_lo.data_ptr());
+  a.m = m.data_ptr<float>();
+  a.v = v.data_ptr<float>();
+  a.sumsq = sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr;
+  a.clip_coef = clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr;
+  a.do_reduce = do_reduce; a.do_update = do_update; a.zero_grads = zero_grads;
+  a.grad_scale = (float)grad_scale; a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
+  a.eps = (float)eps; a.weight_decay = (float)weight_decay; a.step = (int)step;
+  a.sm_count = sm_count();
+  a.stream = cur_stream();
+  c10::cuda::CUDAGuard guard(m.device());
+  zx::launch_zero_step(a);
+  check_launch("zero_step");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -365,6 +475,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope_qkv", &rope_qkv);
+  m.def("rope_bwd_pack", &rope_bwd_pack);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("embedding_fwd", &embedding_fwd);
@@ -375,4 +486,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw", &adamw);
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);
+  m.def("peer_alloc", &peer_alloc);
+  m.def("peer_export", &peer_export);
+  m.def("peer_open", &peer_open);
+  m.def("peer_close", &peer_close);
+  m.def("peer_free", &peer_free);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("peer_pull", &peer_pull);
+  m.def("zero_step", &zero_step);
 }

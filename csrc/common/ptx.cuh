@@ -286,6 +286,37 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_fmt, int b
 }
 
 // ----------------------------------------------------------------------------------------------
+// Fused peer pull: one warp copies this CTA's slice of a (possibly remote) buffer into local
+// memory with 16-byte loads, four in flight per lane. Sizes are in 16-byte vectors.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void warp_pull_slice(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t nvec,
+                                                int lane) {
+  if (src == nullptr || nvec == 0) return;
+  const size_t per = (nvec + gridDim.x - 1) / gridDim.x;
+  const size_t begin = (size_t)blockIdx.x * per;
+  size_t end = begin + per;
+  if (end > nvec) end = nvec;
+  size_t i = begin + lane;
+  for (; i + 96 < end; i += 128) {
+    const uint4 a = ld_stream_v4(src + i), b = ld_stream_v4(src + i + 32), c = ld_stream_v4(src + i + 64),
+                d = ld_stream_v4(src + i + 96);
+    dst[i] = a;
+    dst[i + 32] = b;
+    dst[i + 64] = c;
+    dst[i + 96] = d;
+  }
+  for (; i < end; i += 32) dst[i] = ld_stream_v4(src + i);
+}
+
+// ----------------------------------------------------------------------------------------------
 // Small numeric helpers
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

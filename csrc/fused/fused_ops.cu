@@ -70,7 +70,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw += sum_rows dy * xhat (fp32 atomics per block).
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int H) {
+                                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                                   float* __restrict__ dw_accum, int rows, int H) {
   extern __shared__ float s_dw[];  // [H]
   for (int i = threadIdx.x; i < H; i += blockDim.x) s_dw[i] = 0.f;
   __syncthreads();
@@ -103,6 +104,12 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
         const float xh = fx[j] * r;
         o[j] = r * (fd[j] * fw[j] - xh * dot);
         atomicAdd(&s_dw[i * 8 + j], fd[j] * xh);
+      }
+      if (dres != nullptr) {  // gradient arriving through the residual branch
+        float fr[8];
+        unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * H)[i], fr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += fr[j];
       }
       dxr[i] = pack8(o);
     }
@@ -157,6 +164,53 @@ __global__ void rope_qkv_kernel(__nv_bfloat16* __restrict__ qkv, const float* __
     }
     __nv_bfloat16* dst = src;
     if (h >= Hq && k_out != nullptr) dst = k_out + ((size_t)t * Hkv + (h - Hq)) * D + v * 8;
+    *reinterpret_cast<uint4*>(dst) = pack8(olo);
+    *reinterpret_cast<uint4*>(dst + half) = pack8(ohi);
+  }
+}
+
+// Backward of the QKV split: fp32 dQ [tokens,Hq,D], dK, dV [tokens,Hkv,D] -> bf16 d(qkv)
+// [tokens, (Hq+2Hkv)*D], applying the inverse rotation to the Q and K parts.
+__global__ void rope_bwd_pack_kernel(const float* __restrict__ dq, const float* __restrict__ dk,
+                                     const float* __restrict__ dv, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ dqkv, int tokens,
+                                     int tokens_per_seq, int Hq, int Hkv, int D) {
+  const int half = D >> 1;
+  const int vec_per_head = half >> 3;
+  const int heads = Hq + 2 * Hkv;
+  const size_t total = (size_t)tokens * heads * vec_per_head;
+  const int row_stride = heads * D;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vec_per_head);
+    const int h = (int)((idx / vec_per_head) % heads);
+    const int t = (int)(idx / ((size_t)vec_per_head * heads));
+    const float* src;
+    if (h < Hq) src = dq + ((size_t)t * Hq + h) * D;
+    else if (h < Hq + Hkv) src = dk + ((size_t)t * Hkv + (h - Hq)) * D;
+    else src = dv + ((size_t)t * Hkv + (h - Hq - Hkv)) * D;
+    src += v * 8;
+    float lo[8], hi[8], olo[8], ohi[8];
+    {
+      const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+      const float4 c = reinterpret_cast<const float4*>(src + half)[0], d = reinterpret_cast<const float4*>(src + half)[1];
+      lo[0] = a.x; lo[1] = a.y; lo[2] = a.z; lo[3] = a.w; lo[4] = b.x; lo[5] = b.y; lo[6] = b.z; lo[7] = b.w;
+      hi[0] = c.x; hi[1] = c.y; hi[2] = c.z; hi[3] = c.w; hi[4] = d.x; hi[5] = d.y; hi[6] = d.z; hi[7] = d.w;
+    }
+    if (h < Hq + Hkv) {
+      const int tp = t % tokens_per_seq;
+      const float* cp = cos_t + (size_t)tp * half + v * 8;
+      const float* sp = sin_t + (size_t)tp * half + v * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = cp[j], sj = -sp[j];
+        olo[j] = lo[j] * c - hi[j] * sj;
+        ohi[j] = hi[j] * c + lo[j] * sj;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { olo[j] = lo[j]; ohi[j] = hi[j]; }
+    }
+    __nv_bfloat16* dst = dqkv + (size_t)t * row_stride + (size_t)h * D + v * 8;
     *reinterpret_cast<uint4*>(dst) = pack8(olo);
     *reinterpret_cast<uint4*>(dst + half) = pack8(ohi);
   }
@@ -463,16 +517,16 @@ void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int 
   rmsnorm_fwd_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                                                (__nv_bfloat16*)y, rstd, rows, H, eps);
 }
-void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum,
-                        int rows, int H, int sm_count, cudaStream_t st) {
+void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                        float* dw_accum, int rows, int H, int sm_count, cudaStream_t st) {
   if (rows == 0) return;
   const int threads = 256;
   int grid = sm_count * 4;
   const int max_grid = (rows + 7) / 8;
   if (grid > max_grid) grid = max_grid;
   rmsnorm_bwd_kernel<<<grid, threads, H * sizeof(float), st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                              (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,
-                                                              dw_accum, rows, H);
+                                                              (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+                                                              (__nv_bfloat16*)dx, dw_accum, rows, H);
 }
 void launch_rope_qkv(void* qkv, const float* cos_t, const float* sin_t, void* k_out, void* v_out, int tokens,
                      int tokens_per_seq, int Hq, int Hkv, int D, float sign, int sm_count, cudaStream_t st) {
@@ -482,6 +536,14 @@ void launch_rope_qkv(void* qkv, const float* cos_t, const float* sin_t, void* k_
   rope_qkv_kernel<<<grid_for(total, 256, sm_count), 256, 0, st>>>((__nv_bfloat16*)qkv, cos_t, sin_t,
                                                                   (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, tokens,
                                                                   tokens_per_seq, Hq, Hkv, D, sign);
+}
+void launch_rope_bwd_pack(const float* dq, const float* dk, const float* dv, const float* cos_t, const float* sin_t,
+                          void* dqkv, int tokens, int tokens_per_seq, int Hq, int Hkv, int D, int sm_count,
+                          cudaStream_t st) {
+  if (tokens == 0) return;
+  const size_t total = (size_t)tokens * (Hq + 2 * Hkv) * (D / 16);
+  rope_bwd_pack_kernel<<<grid_for(total, 256, sm_count), 256, 0, st>>>(dq, dk, dv, cos_t, sin_t, (__nv_bfloat16*)dqkv,
+                                                                       tokens, tokens_per_seq, Hq, Hkv, D);
 }
 void launch_swiglu_fwd(const void* gu, void* h, size_t tokens, int F, int sm_count, cudaStream_t st) {
   if (tokens == 0) return;

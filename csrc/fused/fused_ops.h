@@ -8,8 +8,11 @@ namespace zx {
 
 void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H, float eps,
                         cudaStream_t st);
-void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum,
-                        int rows, int H, int sm_count, cudaStream_t st);
+void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                        float* dw_accum, int rows, int H, int sm_count, cudaStream_t st);
+void launch_rope_bwd_pack(const float* dq, const float* dk, const float* dv, const float* cos_t, const float* sin_t,
+                          void* dqkv, int tokens, int tokens_per_seq, int Hq, int Hkv, int D, int sm_count,
+                          cudaStream_t st);
 void launch_rope_qkv(void* qkv, const float* cos_t, const float* sin_t, void* k_out, void* v_out, int tokens,
                      int tokens_per_seq, int Hq, int Hkv, int D, float sign, int sm_count, cudaStream_t st);
 void launch_swiglu_fwd(const void* gu, void* h, size_t tokens, int F, int sm_count, cudaStream_t st);

@@ -1,0 +1,138 @@
+// Reduce-scatter + AdamW + all-gather in one kernel over NVLink peer memory.
+//
+// Each rank owns a contiguous shard of the flat parameter space. For every 4 elements of its shard
+// a thread (1) loads the fp32 gradients of that range from every rank's gradient buffer with P2P
+// loads and sums them (the reduce-scatter), (2) applies the scale / clip factor and the AdamW
+// update to its fp32 master weight (kept as bf16 high half + int16 remainder), and (3) stores the
+// new bf16 parameter into every rank's parameter buffer with P2P stores (the all-gather). No
+// intermediate buffer, no NCCL. The two halves can also run as separate launches (reduce, then
+// update) when a global gradient norm is needed in between.
+// The reference does this as bucketed all-reduce + copy-back + torch AdamW
+// (zenyx/runtime/scheduler.py:32-107,158-160).
+#include "../common/ptx.cuh"
+#include "zero.h"
+
+namespace zx {
+
+namespace {
+
+struct ZParams {
+  PeerPtrs grads, params;
+  int nranks, rank;
+  size_t shard_begin, n_shard, decay_end;
+  float* g_shard;
+  int16_t* p_lo;
+  float* m;
+  float* v;
+  float* sumsq;
+  const float* clip_coef;
+  int do_reduce, do_update, zero_grads;
+  float grad_scale, lr, beta1, beta2, eps, weight_decay, bias1, bias2;
+};
+
+__device__ __forceinline__ float4 ld_f4_stream(const float* p) {
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
+  __shared__ float s_red[8];
+  const size_t nvec = p.n_shard >> 2;
+  float local_ss = 0.f;
+  const float clip = (p.do_update && p.clip_coef != nullptr) ? *p.clip_coef : 1.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t gi = p.shard_begin + (i << 2);  // global element index
+    float4 g;
+    if (p.do_reduce) {
+      g = make_float4(0.f, 0.f, 0.f, 0.f);
+      // start with the next rank so the R readers of one step hit R different owners
+      for (int k = 0; k < p.nranks; ++k) {
+        int r = p.rank + 1 + k;
+        if (r >= p.nranks) r -= p.nranks;
+        float* src = reinterpret_cast<float*>(p.grads.p[r]) + gi;
+        const float4 a = ld_f4_stream(src);
+        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+        if (p.zero_grads) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      g.x *= p.grad_scale; g.y *= p.grad_scale; g.z *= p.grad_scale; g.w *= p.grad_scale;
+      local_ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+      if (!p.do_update) {
+        reinterpret_cast<float4*>(p.g_shard)[i] = g;
+        continue;
+      }
+    } else {
+      g = reinterpret_cast<const float4*>(p.g_shard)[i];
+    }
+    // ---- AdamW on the split master ----
+    g.x *= clip; g.y *= clip; g.z *= clip; g.w *= clip;
+    uint16_t* own_params = reinterpret_cast<uint16_t*>(p.params.p[p.rank]);
+    const uint2 hi = *reinterpret_cast<const uint2*>(own_params + gi);
+    const uint2 lo = reinterpret_cast<const uint2*>(p.p_lo)[i];
+    float4 mm = reinterpret_cast<float4*>(p.m)[i];
+    float4 vv = reinterpret_cast<float4*>(p.v)[i];
+    const uint16_t h[4] = {(uint16_t)(hi.x & 0xffff), (uint16_t)(hi.x >> 16), (uint16_t)(hi.y & 0xffff), (uint16_t)(hi.y >> 16)};
+    const int16_t l[4] = {(int16_t)(lo.x & 0xffff), (int16_t)(lo.x >> 16), (int16_t)(lo.y & 0xffff), (int16_t)(lo.y >> 16)};
+    float gr[4] = {g.x, g.y, g.z, g.w};
+    float ma[4] = {mm.x, mm.y, mm.z, mm.w};
+    float va[4] = {vv.x, vv.y, vv.z, vv.w};
+    const float wd = gi < p.decay_end ? p.weight_decay : 0.f;
+    uint32_t nh[4], nl[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float w = __uint_as_float(((uint32_t)h[j] << 16) + (uint32_t)(int32_t)l[j]);
+      ma[j] = p.beta1 * ma[j] + (1.f - p.beta1) * gr[j];
+      va[j] = p.beta2 * va[j] + (1.f - p.beta2) * gr[j] * gr[j];
+      w = w * (1.f - p.lr * wd) - p.lr * (ma[j] / p.bias1) / (sqrtf(va[j] / p.bias2) + p.eps);
+      const uint32_t bits = __float_as_uint(w);
+      const uint32_t hh = (bits + 0x8000u) >> 16;
+      nh[j] = hh & 0xffffu;
+      nl[j] = (bits - (hh << 16)) & 0xffffu;
+    }
+    reinterpret_cast<float4*>(p.m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+    reinterpret_cast<float4*>(p.v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+    reinterpret_cast<uint2*>(p.p_lo)[i] = make_uint2(nl[0] | (nl[1] << 16), nl[2] | (nl[3] << 16));
+    const uint2 new_hi = make_uint2(nh[0] | (nh[1] << 16), nh[2] | (nh[3] << 16));
+    // all-gather: push the new bf16 parameters into every rank's buffer
+    for (int r = 0; r < p.nranks; ++r)
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.params.p[r]) + gi) = new_hi;
+  }
+  if (p.do_reduce && p.sumsq != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local_ss += __shfl_xor_sync(0xffffffffu, local_ss, o);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = local_ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s_red[w];
+      atomicAdd(p.sumsq, t);
+    }
+  }
+}
+
+}  // namespace
+
+void launch_zero_step(const ZeroArgs& a) {
+  if (a.n_shard == 0) return;
+  ZParams p;
+  p.grads = a.grads; p.params = a.params;
+  p.nranks = a.nranks; p.rank = a.rank;
+  p.shard_begin = a.shard_begin; p.n_shard = a.n_shard; p.decay_end = a.decay_end;
+  p.g_shard = a.g_shard; p.p_lo = a.p_lo; p.m = a.m; p.v = a.v;
+  p.sumsq = a.sumsq; p.clip_coef = a.clip_coef;
+  p.do_reduce = a.do_reduce; p.do_update = a.do_update; p.zero_grads = a.zero_grads;
+  p.grad_scale = a.grad_scale; p.lr = a.lr; p.beta1 = a.beta1; p.beta2 = a.beta2; p.eps = a.eps;
+  p.weight_decay = a.weight_decay;
+  p.bias1 = 1.f - powf(a.beta1, (float)a.step);
+  p.bias2 = 1.f - powf(a.beta2, (float)a.step);
+  const size_t nvec = a.n_shard / 4;
+  size_t blocks = (nvec + 255) / 256;
+  const size_t cap = (size_t)a.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  zero_step_kernel<<<(unsigned)blocks, 256, 0, a.stream>>>(p);
+}
+
+}  // namespace zx

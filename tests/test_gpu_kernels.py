@@ -112,7 +112,7 @@ def test_attn_fwd_basic(C, causal, B, S, Hq, Hkv):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False)
+    C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False, 0, 0, 0)
     _status_ok()
     pos = torch.arange(S, device="cuda")
     o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, causal)
@@ -131,7 +131,7 @@ def test_attn_fwd_strided_qkv_and_long(C):
     o = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    C.attn_fwd(q, k, v, o, lse, scale, True, 0, 0, [0], [0], False)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 0, 0, [0], [0], False, 0, 0, 0)
     _status_ok()
     pos = torch.arange(S, device="cuda")
     o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, True)
@@ -163,7 +163,7 @@ def test_attn_fwd_zigzag_ring_merge(C):
         qpos = [c * L for c in chunks[r]]
         for step, owner in enumerate([r, 1 - r]):
             C.attn_fwd(qr, shard(k, owner), shard(v, owner), o, lse, scale, True, 0, 0, qpos,
-                       [c * L for c in chunks[owner]], step > 0)
+                       [c * L for c in chunks[owner]], step > 0, 0, 0, 0)
         _status_ok()
         o_exp = shard(o_ref, r)
         lse_exp = torch.cat([lse_ref[:, :, c * L : (c + 1) * L] for c in chunks[r]], dim=2)
@@ -180,7 +180,7 @@ def test_attn_fwd_block_sparse(C):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    C.attn_fwd(q, k, v, o, lse, scale, True, 3, 4, [0], [0], False)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 3, 4, [0], [0], False, 0, 0, 0)
     _status_ok()
     pos = torch.arange(S, device="cuda")
     o_ref, lse_ref = _attn_ref(q, k, v, scale, pos, pos, True, 3, 4)
@@ -204,7 +204,7 @@ def test_rmsnorm(C):
     ref.backward(dy.float())
     dx = torch.empty_like(x)
     dw = torch.zeros(H, device="cuda")
-    C.rmsnorm_bwd(dy, x, w, rstd, dx, dw)
+    C.rmsnorm_bwd(dy, x, w, rstd, dx, dw, None)
     assert _rel_err(dx, xf.grad) < 1e-2
     assert _rel_err(dw, wf.grad) < 1e-2
 
@@ -344,12 +344,12 @@ def test_attn_bwd_basic(C, causal, B, S, Hq, Hkv):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False)
+    C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False, 0, 0, 0)
     delta = torch.empty_like(lse)
     dq = torch.empty(B, S, Hq, D, device="cuda")
     dk = torch.zeros(B, S, Hkv, D, device="cuda")
     dv = torch.zeros(B, S, Hkv, D, device="cuda")
-    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, causal, 0, 0, [0], [0], True, False)
+    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, causal, 0, 0, [0], [0], True, False, 0, 0, 0)
     _status_ok()
     pos = torch.arange(S, device="cuda")
     dq_r, dk_r, dv_r = _attn_bwd_ref(q, k, v, do, scale, pos, pos, causal)
@@ -386,12 +386,12 @@ def test_attn_bwd_zigzag_ring(C):
         order = [r, 1 - r]
         for step, owner in enumerate(order):
             C.attn_fwd(qr, shard(k, owner), shard(v, owner), o, lse, scale, True, 0, 0, qpos,
-                       [c * L for c in chunks[owner]], step > 0)
+                       [c * L for c in chunks[owner]], step > 0, 0, 0, 0)
         delta = torch.empty_like(lse)
         dq = torch.empty(B, 2 * L, Hq, D, device="cuda")
         for step, owner in enumerate(order):
             C.attn_bwd(qr, shard(k, owner), shard(v, owner), o, dor, lse, delta, dq, dk_own[owner], dv_own[owner],
-                       scale, True, 0, 0, qpos, [c * L for c in chunks[owner]], step == 0, step > 0)
+                       scale, True, 0, 0, qpos, [c * L for c in chunks[owner]], step == 0, step > 0, 0, 0, 0)
         _status_ok()
         assert _rel_err(dq, shard(dq_r, r)) < 2e-2
     for r in (0, 1):
@@ -409,12 +409,12 @@ def test_attn_bwd_block_sparse(C):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    C.attn_fwd(q, k, v, o, lse, scale, True, 2, 4, [0], [0], False)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 2, 4, [0], [0], False, 0, 0, 0)
     delta = torch.empty_like(lse)
     dq = torch.empty(B, S, Hq, D, device="cuda")
     dk = torch.zeros(B, S, Hkv, D, device="cuda")
     dv = torch.zeros(B, S, Hkv, D, device="cuda")
-    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, True, 2, 4, [0], [0], True, False)
+    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, True, 2, 4, [0], [0], True, False, 0, 0, 0)
     _status_ok()
     pos = torch.arange(S, device="cuda")
     dq_r, dk_r, dv_r = _attn_bwd_ref(q, k, v, do, scale, pos, pos, True, 2, 4)

@@ -83,7 +83,7 @@ def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    ms_f = time_cuda(lambda: C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False), iters=5)
+    ms_f = time_cuda(lambda: C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False, 0, 0, 0), iters=5)
     _ext.check_status()
     flops_f = 4.0 * B * Hq * S * S * D * (0.5 if causal else 1.0)
     rec = {"kernel": "attn_fwd", "S": S, "Hq": Hq, "Hkv": Hkv, "B": B, "causal": causal, "ms": round(ms_f, 3),
@@ -96,7 +96,7 @@ def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True):
         dk = torch.zeros(B, S, Hkv, D, device="cuda")
         dv = torch.zeros(B, S, Hkv, D, device="cuda")
         ms_b = time_cuda(lambda: C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, causal, 0, 0, [0], [0],
-                                            True, False), iters=5)
+                                            True, False, 0, 0, 0), iters=5)
         _ext.check_status()
         flops_b = 2.5 * flops_f
         out.append({"kernel": "attn_bwd", "S": S, "Hq": Hq, "Hkv": Hkv, "B": B, "causal": causal,
