@@ -1,0 +1,420 @@
+"""Belady-optimal HBM / DRAM / NVMe tiering of the KV cache.
+
+The module path keeps the reference's spelling (``zenyx.train.belayd_kv_cache_tiering``,
+README.md:61). The reference documents ``BeladyKVCacheTieringManager(num_devices=8,
+context_length=4096, num_layers=12)`` and ``RingAttentionAccessSequence`` ("three-tier memory
+hierarchy", "offline-optimal page replacement", "completely predictable access patterns from ring
+attention", README.md:93-97,150-154,343) without shipping them; what survives is an item-counting
+approximation fed by the caller (zenyx/streaming/belady.py:8-58), an LRU host tier and a dict
+labelled "disk" (zenyx/streaming/kv_tiering.py:11-73).
+
+Here the access order is generated from the ring schedule itself (every reader of every block at
+every ring step of every layer, forward then backward), the residency plan is true Belady MIN over
+*bytes* (C++: csrc/tier/belady_min.cpp), and the manager executes that plan: blocks live in HBM, in
+pinned host memory or in a file; a miss that the plan foresees is prefetched on a side stream
+(pinned ``cudaMemcpyAsync``) ``lookahead`` accesses ahead of its use, and the time a consumer
+actually had to wait is accounted as exposed stall. Without CUDA (or ``simulate=True``) the same
+plan is replayed against bandwidth figures instead of moving bytes.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import _ext
+from ..ops.attention import MaskSpec, shard_positions, step_has_work
+
+
+@dataclass(frozen=True)
+class Access:
+    t: int        # time slot (one per layer x ring step x phase)
+    layer: int
+    owner: int    # device whose HBM holds the block
+    block: int    # block index within the owner's shard
+    reader: int   # device whose attention kernel reads it
+    phase: str    # "forward" | "backward"
+
+
+class RingAttentionAccessSequence:
+    """The deterministic order in which ring attention touches KV blocks.
+
+    Generalises the reference's ``build_ring_timeline`` (forward ascending, backward reversed,
+    zenyx/streaming/kv_tiering.py:69-73). At ring step s device r reads the blocks of device
+    (r - s) mod R; with a sparse pattern, steps without a kept tile are dropped.
+    """
+
+    def __init__(self, num_devices: int, num_layers: int, blocks_per_device: int, *, zigzag: bool = True,
+                 sparse_pattern=None, phases: Sequence[str] = ("forward", "backward"), seq_len: Optional[int] = None):
+        self.num_devices, self.num_layers, self.blocks_per_device = num_devices, num_layers, blocks_per_device
+        self.zigzag, self.sparse_pattern, self.phases = zigzag, sparse_pattern, tuple(phases)
+        self.seq_len = seq_len
+        self._accesses: Optional[List[Access]] = None
+
+    def _step_active(self, reader: int, step: int) -> bool:
+        if self.sparse_pattern is None or self.seq_len is None:
+            return True
+        R = self.num_devices
+        layout = "zigzag" if self.zigzag else "contiguous"
+        local = self.seq_len // R
+        mask: MaskSpec = self.sparse_pattern.mask_spec() if hasattr(self.sparse_pattern, "mask_spec") else self.sparse_pattern
+        owner = (reader - step) % R
+        return step_has_work(mask, shard_positions(reader, R, self.seq_len, layout), local,
+                             shard_positions(owner, R, self.seq_len, layout), local)
+
+    def accesses(self) -> List[Access]:
+        if self._accesses is not None:
+            return self._accesses
+        out: List[Access] = []
+        t = 0
+        R = self.num_devices
+        for phase in self.phases:
+            layers = range(self.num_layers) if phase == "forward" else reversed(range(self.num_layers))
+            for layer in layers:
+                for step in range(R):
+                    for reader in range(R):
+                        if not self._step_active(reader, step):
+                            continue
+                        owner = (reader - step) % R
+                        for b in range(self.blocks_per_device):
+                            out.append(Access(t, layer, owner, b, reader, phase))
+                    t += 1
+        self._accesses = out
+        return out
+
+    def for_device(self, rank: int) -> List[Access]:
+        """Accesses that touch blocks held by `rank` (its own reads and every peer's reads)."""
+        return [a for a in self.accesses() if a.owner == rank]
+
+    def block_ids(self, rank: int) -> List[int]:
+        """Dense ids (layer * blocks_per_device + block) of for_device(rank), in order."""
+        return [a.layer * self.blocks_per_device + a.block for a in self.for_device(rank)]
+
+    def next_use(self, rank: int, layer: int, block: int, t: int) -> Optional[int]:
+        for a in self.for_device(rank):
+            if a.t > t and a.layer == layer and a.block == block:
+                return a.t
+        return None
+
+    def __len__(self) -> int:
+        return len(self.accesses())
+
+
+@dataclass
+class TierPlan:
+    ids: List[int]                      # block id per access
+    hit: List[bool]
+    evict_before: List[List[int]]       # blocks to drop from HBM right before serving access i
+    next_use: List[int]
+    hits: int
+    misses: int
+    bytes_loaded: int
+    bytes_evicted: int
+    peak_resident_bytes: int
+    bypassed: int
+    block_bytes: int
+    capacity_bytes: int
+
+    @property
+    def hit_rate(self) -> float:
+        return self.hits / max(1, self.hits + self.misses)
+
+
+@dataclass
+class TierStats:
+    hits: int = 0
+    misses: int = 0
+    bytes_h2d: int = 0
+    bytes_d2h: int = 0
+    bytes_nvme_read: int = 0
+    bytes_nvme_write: int = 0
+    exposed_stall_ms: float = 0.0
+    prefetched: int = 0
+    peak_hbm_bytes: int = 0
+    accesses: int = 0
+
+    def as_dict(self) -> Dict[str, float]:
+        return dict(self.__dict__)
+
+
+class BeladyKVCacheTieringManager:
+    """Plans and (on a GPU) executes KV-block residency for one device of a ring.
+
+    A *block* is ``tier_block_tokens`` tokens of K and V of one layer:
+    ``2 * tier_block_tokens * num_kv_heads * head_dim * itemsize`` bytes. The device owns
+    ``context_length / num_devices`` tokens per layer. Peers read this device's blocks out of its
+    HBM at known ring steps, so the plan covers every reader's accesses, not only the local ones.
+    """
+
+    def __init__(self, num_devices: int = 8, context_length: int = 4096, num_layers: int = 12, *,
+                 num_kv_heads: int = 8, head_dim: int = 128, dtype: torch.dtype = torch.bfloat16,
+                 tier_block_tokens: Optional[int] = None, hbm_budget_bytes: int = 16 << 30,
+                 dram_budget_bytes: Optional[int] = None, nvme_path: Optional[str] = None,
+                 simulate: Optional[bool] = None, rank: int = 0, lookahead: int = 4, sparse_pattern=None,
+                 zigzag: bool = True):
+        self.num_devices, self.context_length, self.num_layers = num_devices, context_length, num_layers
+        self.num_kv_heads, self.head_dim, self.dtype, self.rank = num_kv_heads, head_dim, dtype, rank
+        self.local_tokens = context_length // num_devices
+        if tier_block_tokens is None:
+            tier_block_tokens = min(self.local_tokens, 4096)
+        if self.local_tokens % tier_block_tokens != 0:
+            raise ValueError("tier_block_tokens must divide the per-device token count")
+        self.tier_block_tokens = tier_block_tokens
+        self.blocks_per_layer = self.local_tokens // tier_block_tokens
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        self.block_elems = 2 * tier_block_tokens * num_kv_heads * head_dim
+        self.block_bytes = self.block_elems * itemsize
+        self.hbm_budget_bytes = int(hbm_budget_bytes)
+        self.dram_budget_bytes = dram_budget_bytes
+        self.nvme_path = nvme_path
+        self.simulate_mode = (not torch.cuda.is_available()) if simulate is None else bool(simulate)
+        self.lookahead = lookahead
+        self._seq = RingAttentionAccessSequence(num_devices, num_layers, self.blocks_per_layer, zigzag=zigzag,
+                                                sparse_pattern=sparse_pattern, seq_len=context_length)
+        self._plan: Optional[TierPlan] = None
+        self._stats = TierStats()
+        # execution state (real mode)
+        self._hbm: Dict[int, torch.Tensor] = {}
+        self._dram: Dict[int, torch.Tensor] = {}
+        self._on_disk: Dict[int, int] = {}           # block id -> file slot
+        self._inflight: Dict[int, "torch.cuda.Event"] = {}
+        self._cursor = 0
+        self._copy_stream = None
+        self._file = None
+        self._bounce: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------------------------------
+    def access_sequence(self) -> RingAttentionAccessSequence:
+        return self._seq
+
+    def block_id(self, layer: int, block: int) -> int:
+        return layer * self.blocks_per_layer + block
+
+    def plan(self) -> TierPlan:
+        if self._plan is not None:
+            return self._plan
+        ids = self._seq.block_ids(self.rank)
+        n_blocks = self.num_layers * self.blocks_per_layer
+        res = _ext.host().belady_min(ids, [self.block_bytes] * n_blocks, self.hbm_budget_bytes)
+        self._plan = TierPlan(ids=ids, hit=[bool(h) for h in res["hit"]], evict_before=[list(e) for e in res["evicted"]],
+                              next_use=[int(x) for x in res["next_use"]], hits=int(res["hits"]),
+                              misses=int(res["misses"]), bytes_loaded=int(res["bytes_loaded"]),
+                              bytes_evicted=int(res["bytes_evicted"]),
+                              peak_resident_bytes=int(res["peak_resident_bytes"]), bypassed=int(res["bypassed"]),
+                              block_bytes=self.block_bytes, capacity_bytes=self.hbm_budget_bytes)
+        return self._plan
+
+    def lru_baseline(self) -> Dict[str, int]:
+        """The same trace under LRU (what the reference's host tier does), for comparison."""
+        ids = self._seq.block_ids(self.rank)
+        res = _ext.host().lru_trace(ids, [self.block_bytes] * (self.num_layers * self.blocks_per_layer),
+                                    self.hbm_budget_bytes)
+        return {"hits": int(res["hits"]), "misses": int(res["misses"]), "bytes_loaded": int(res["bytes_loaded"])}
+
+    def total_kv_bytes(self) -> int:
+        return self.num_layers * self.blocks_per_layer * self.block_bytes
+
+    # ------------------------------------------------------------------------------------------
+    # simulation: replay the plan against bandwidths
+    # ------------------------------------------------------------------------------------------
+    def simulate(self, bandwidths: Optional[Dict[str, float]] = None, compute_ms_per_access: float = 1.0) -> TierStats:
+        """Replays the plan. ``bandwidths`` = {"pcie_gbs", "nvme_gbs"}; a miss is prefetched
+        ``lookahead`` accesses early, and only the part of its transfer that is not covered by
+        the compute of those accesses counts as exposed stall. Blocks that do not fit the DRAM
+        budget are charged at NVMe speed."""
+        bw = {"pcie_gbs": 50.0, "nvme_gbs": 6.0}
+        bw.update(bandwidths or {})
+        plan = self.plan()
+        st = TierStats(accesses=len(plan.ids), hits=plan.hits, misses=plan.misses,
+                       peak_hbm_bytes=plan.peak_resident_bytes)
+        dram_cap = self.dram_budget_bytes if self.dram_budget_bytes is not None else float("inf")
+        spilled = max(0, self.total_kv_bytes() - self.hbm_budget_bytes)
+        nvme_fraction = 0.0 if spilled <= dram_cap or spilled == 0 else (spilled - dram_cap) / spilled
+        link_free_at = 0.0   # the copy engine is serial
+        now = 0.0
+        for i, is_hit in enumerate(plan.hit):
+            if not is_hit:
+                t_pcie = self.block_bytes / (bw["pcie_gbs"] * 1e6)
+                t_nvme = self.block_bytes / (bw["nvme_gbs"] * 1e6)
+                xfer = t_pcie + nvme_fraction * t_nvme
+                issue = max(link_free_at, now - self.lookahead * compute_ms_per_access)
+                done = issue + xfer
+                link_free_at = done
+                if done > now:
+                    st.exposed_stall_ms += done - now
+                    now = done
+                else:
+                    st.prefetched += 1
+                st.bytes_h2d += self.block_bytes
+                st.bytes_nvme_read += int(nvme_fraction * self.block_bytes)
+            st.bytes_d2h += self.block_bytes * len(plan.evict_before[i])
+            now += compute_ms_per_access
+        self._stats = st
+        return st
+
+    # ------------------------------------------------------------------------------------------
+    # execution on a GPU
+    # ------------------------------------------------------------------------------------------
+    def _ensure_runtime(self) -> None:
+        if self.simulate_mode:
+            raise RuntimeError("this manager is in simulation mode (no CUDA device, or simulate=True)")
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream()
+        if self.nvme_path is not None and self._file is None:
+            os.makedirs(os.path.dirname(os.path.abspath(self.nvme_path)) or ".", exist_ok=True)
+            slots = self.num_layers * self.blocks_per_layer
+            self._file = _ext.host().FileTier(self.nvme_path, self.block_bytes, slots, 2, self.block_bytes % 4096 == 0)
+            self._bounce = torch.empty(self.block_elems, dtype=self.dtype).pin_memory()
+
+    def _hbm_bytes(self) -> int:
+        return len(self._hbm) * self.block_bytes
+
+    def _dram_has_room(self) -> bool:
+        cap = self.dram_budget_bytes
+        return cap is None or (len(self._dram) + 1) * self.block_bytes <= cap
+
+    def register(self, layer: int, block: int, tensor: torch.Tensor) -> None:
+        """Hands a freshly produced K|V block (``block_elems`` elements on the GPU) to the manager."""
+        self._ensure_runtime()
+        bid = self.block_id(layer, block)
+        flat = tensor.reshape(-1)
+        assert flat.numel() == self.block_elems and flat.is_cuda, "block has the wrong size or device"
+        spills = self.total_kv_bytes() > self.hbm_budget_bytes
+        if self._hbm_bytes() + self.block_bytes <= self.hbm_budget_bytes:
+            self._hbm[bid] = flat
+            self._stats.peak_hbm_bytes = max(self._stats.peak_hbm_bytes, self._hbm_bytes())
+        if not spills:
+            return
+        # write-through to the lower tiers, so that evicting from HBM later is free
+        self._copy_stream.wait_stream(torch.cuda.current_stream())
+        if self._dram_has_room():
+            host = torch.empty(self.block_elems, dtype=self.dtype).pin_memory()
+            with torch.cuda.stream(self._copy_stream):
+                host.copy_(flat, non_blocking=True)
+            flat.record_stream(self._copy_stream)
+            self._dram[bid] = host
+            self._stats.bytes_d2h += self.block_bytes
+        elif self._file is not None:
+            with torch.cuda.stream(self._copy_stream):
+                self._bounce.copy_(flat, non_blocking=True)
+            self._copy_stream.synchronize()
+            ticket = self._file.write_async(bid, self._bounce.data_ptr(), self.block_bytes)
+            if self._file.wait(ticket) != 0:
+                raise IOError(f"writing KV block {bid} to {self.nvme_path} failed")
+            self._on_disk[bid] = bid
+            self._stats.bytes_d2h += self.block_bytes
+            self._stats.bytes_nvme_write += self.block_bytes
+        else:
+            raise MemoryError("KV does not fit the HBM and DRAM budgets and no nvme_path was given")
+
+    def _start_load(self, bid: int) -> None:
+        """Begins bringing block `bid` into HBM on the copy stream."""
+        if bid in self._hbm or bid in self._inflight:
+            return
+        dev = torch.empty(self.block_elems, dtype=self.dtype, device="cuda")
+        if bid in self._dram:
+            src = self._dram[bid]
+        elif bid in self._on_disk:
+            ticket = self._file.read_async(bid, self._bounce.data_ptr(), self.block_bytes)
+            if self._file.wait(ticket) != 0:
+                raise IOError(f"reading KV block {bid} from {self.nvme_path} failed")
+            self._stats.bytes_nvme_read += self.block_bytes
+            src = self._bounce
+        else:
+            raise KeyError(f"KV block {bid} was never registered")
+        with torch.cuda.stream(self._copy_stream):
+            dev.copy_(src, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        if src is self._bounce:
+            ev.synchronize()  # the bounce buffer is reused by the next file read
+        self._hbm[bid] = dev
+        self._inflight[bid] = ev
+        self._stats.bytes_h2d += self.block_bytes
+        self._stats.peak_hbm_bytes = max(self._stats.peak_hbm_bytes, self._hbm_bytes())
+
+    def step_begin(self) -> None:
+        self._cursor = 0
+
+    def acquire(self, layer: int, block: int, stream: Optional["torch.cuda.Stream"] = None) -> torch.Tensor:
+        """Returns the block as a GPU tensor, following the plan: evict what the plan evicts here,
+        wait for (or start) its load, and start the loads of the next foreseen misses."""
+        self._ensure_runtime()
+        plan = self.plan()
+        bid = self.block_id(layer, block)
+        i = self._cursor
+        in_order = i < len(plan.ids) and plan.ids[i] == bid
+        if in_order:
+            for victim in plan.evict_before[i]:
+                if victim != bid and victim not in self._inflight:
+                    self._hbm.pop(victim, None)
+            self._cursor += 1
+        self._stats.accesses += 1
+        if bid in self._hbm and bid not in self._inflight:
+            self._stats.hits += 1
+        else:
+            self._stats.misses += 1
+            if bid not in self._hbm:
+                while self._hbm_bytes() + self.block_bytes > self.hbm_budget_bytes and self._hbm:
+                    # out-of-plan request: drop the resident block whose next planned use is farthest
+                    far = max((b for b in self._hbm if b not in self._inflight),
+                              key=lambda b: self._next_planned_use(b), default=None)
+                    if far is None:
+                        break
+                    self._hbm.pop(far)
+                self._start_load(bid)
+        ev = self._inflight.pop(bid, None)
+        if ev is not None:
+            if not ev.query():
+                t0 = time.perf_counter()
+                ev.synchronize()
+                self._stats.exposed_stall_ms += (time.perf_counter() - t0) * 1e3
+            else:
+                self._stats.prefetched += 1
+            (stream or torch.cuda.current_stream()).wait_event(ev)
+        if in_order:
+            self._prefetch_ahead()
+        return self._hbm[bid]
+
+    def _next_planned_use(self, bid: int) -> int:
+        plan = self.plan()
+        for j in range(self._cursor, len(plan.ids)):
+            if plan.ids[j] == bid:
+                return j
+        return len(plan.ids) + 1
+
+    def _prefetch_ahead(self) -> None:
+        plan = self.plan()
+        end = min(len(plan.ids), self._cursor + self.lookahead)
+        for j in range(self._cursor, end):
+            bid = plan.ids[j]
+            if bid in self._hbm:
+                continue
+            if self._hbm_bytes() + self.block_bytes > self.hbm_budget_bytes:
+                break
+            self._start_load(bid)
+
+    def release(self, layer: int, block: int) -> None:  # noqa: ARG002
+        """Blocks stay resident until the plan evicts them; nothing to do."""
+
+    def step_end(self) -> None:
+        if self._copy_stream is not None:
+            self._copy_stream.synchronize()
+        self._inflight.clear()
+
+    def stats(self) -> TierStats:
+        return self._stats
+
+    def close(self) -> None:
+        self.step_end()
+        self._hbm.clear()
+        self._dram.clear()
+        self._file = None
+        if self.nvme_path and os.path.exists(self.nvme_path):
+            os.remove(self.nvme_path)
+
+
+__all__ = ["Access", "RingAttentionAccessSequence", "TierPlan", "TierStats", "BeladyKVCacheTieringManager"]
