@@ -1,7 +1,7 @@
 // Flash-attention forward for sm_100a (head_dim 128, bf16 in, fp32 softmax/accumulate).
 //
 // One CTA owns two adjacent 128-row Q tiles of one head and walks the KV buffer once:
-//   warp 8      TMA producer: Q once, then K/V tiles through a 2-stage ring (non-multicast loads)
+//   warp 8      TMA producer: Q once, then K/V tiles through a 2-stage ring (plain per-CTA loads)
 //   warp 9      MMA issuer:   S_i = Q_i K^T  (SS form) and O_i += P_i V (A = P read from TMEM)
 //   warp 10     optional peer pull: copies this CTA's slice of the next ring step's K/V from the
 //               owning GPU into local staging with plain P2P loads while the tiles compute

@@ -1,4 +1,4 @@
-// Thin inline-PTX layer for sm_100a: mbarrier, TMA (non-multicast only), tcgen05 MMA / TMEM.
+// Thin inline-PTX layer for sm_100a: mbarrier, TMA (per-CTA loads only), tcgen05 MMA / TMEM.
 // Everything here is header-only and free of torch includes so kernels compile in seconds.
 #pragma once
 #include <cuda.h>
@@ -105,7 +105,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ----------------------------------------------------------------------------------------------
-// TMA (tiled bulk tensor copies). Loads are always CTA-local destinations, never multicast.
+// TMA (tiled bulk tensor copies). Every load targets the issuing CTA only.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

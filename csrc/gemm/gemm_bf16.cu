@@ -1,6 +1,6 @@
 // Persistent bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T (+ D), fp32 accumulation in TMEM.
 //
-//  * operands are staged by TMA (128-byte swizzle, non-multicast) through a 4-deep mbarrier ring,
+//  * operands are staged by TMA (128-byte swizzle, per-CTA loads) through a 4-deep mbarrier ring,
 //  * one elected thread issues tcgen05.mma 128x256x16 into one of two 256-column TMEM accumulators,
 //  * four epilogue warps drain the other accumulator with tcgen05.ld while the next tile computes.
 //
