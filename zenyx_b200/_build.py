@@ -33,7 +33,7 @@ CUDA_SOURCES = [
     "fused/fused_ops.cu",
     "peer/peer_kernels.cu",
     "optim/zero_adamw.cu",
-    "noalloc/sumsq_static.cu",
+    "noalloc/attn_bwd_static.cu",
 ]
 CUDA_CPP_SOURCES = ["bindings.cpp", "peer/ipc_memory.cpp"]
 HOST_SOURCES = ["tier/belady_min.cpp", "tier/tier_engine.cpp", "cpu_ref/flash_cpu.cpp", "host_bindings.cpp"]
