@@ -1,0 +1,78 @@
+"""Every public name of the reference package is importable from this one."""
+import importlib
+
+import pytest
+
+
+def test_top_level_names():
+    import zenyx_b200 as z
+
+    for name in ["Scheduler", "ExecutionPlan", "ExecutionGraph", "ExecutionGraphBuilder", "OpNode", "OpType",
+                 "FSDPWrapper", "ActivationManager", "OffloadManager", "OffloadPolicy", "make_offload_policy",
+                 "setup_logging", "get_logger", "Trainer", "TrainerConfig"]:
+        assert getattr(z, name) is not None, name
+    for name in z.__all__:
+        assert hasattr(z, name), name
+
+
+@pytest.mark.parametrize("module,names", [
+    ("zenyx_b200.utils", ["setup_logging", "get_logger", "set_log_level"]),
+    ("zenyx_b200.distributed", ["init_process_group", "init_distributed_from_env", "destroy_process_group", "all_reduce",
+                                "broadcast", "barrier", "get_rank", "get_world_size", "AsyncCollectiveHandle",
+                                "CollectiveGroup", "DistributedContext", "CommunicationError", "FSDPWrapper",
+                                "ColumnParallelLinear", "RowParallelLinear", "TensorParallelEmbedding",
+                                "make_tensor_parallel_model", "PipelineStage", "DistributedPipelineEngine",
+                                "PipelineParallelModel", "create_pipeline_from_sequential", "SimpleGPipeSchedule",
+                                "Partial1F1BSchedule"]),
+    ("zenyx_b200.memory", ["ActivationManager", "CheckpointPolicy", "MemoryTracker", "MemorySnapshot"]),
+    ("zenyx_b200.compiler", ["ExecutionGraph", "GraphNode", "OffloadPolicy", "OffloadManager", "make_offload_policy",
+                             "XLACheckpointPolicy", "remat_or_checkpoint", "maybe_offload_large_tensor"]),
+    ("zenyx_b200.streaming", ["StreamingExecutionEngine", "StreamingConfig", "LayerWeightStreamer", "ParameterStore",
+                              "KVTierManager", "build_ring_timeline", "BeladyApproxCache", "BandwidthAwareScheduler",
+                              "BandwidthSample", "quantize_to_fp8_storage", "dequantize_for_bf16_compute"]),
+    ("zenyx_b200.runtime", ["ExecutionGraph", "ExecutionGraphBuilder", "OpNode", "OpType", "Scheduler", "ExecutionPlan",
+                            "TopologyConfig", "GraphValidator", "validate_graph", "ValidationError", "ValidationResult"]),
+    ("zenyx_b200.train", ["Trainer", "TrainerConfig", "load_state_dict_chunked"]),
+    ("zenyx_b200.train.belayd_kv_cache_tiering", ["BeladyKVCacheTieringManager", "RingAttentionAccessSequence"]),
+    ("zenyx_b200.train.fp8_kv_quantization", ["FP8KVQuantizer", "QuantizedRingAttention"]),
+    ("zenyx_b200.train.dynamic_ring_curriculum", ["RingDegreeScheduler", "CurriculumPhase"]),
+    ("zenyx_b200.train.sparse_ring_attention", ["SparseRingAttention", "SparsePattern"]),
+    ("zenyx_b200.core.distributed", ["DistributedTrainingManager"]),
+    ("zenyx_b200.core.hardware", ["HardwareDetector"]),
+    ("zenyx_b200.planner", ["plan", "ParallelPlan"]),
+])
+def test_module_names(module, names):
+    m = importlib.import_module(module)
+    for n in names:
+        assert hasattr(m, n), f"{module}.{n}"
+
+
+def test_star_import_works():
+    ns = {}
+    exec("from zenyx_b200 import *", ns)
+    assert "OpType" in ns and "Scheduler" in ns
+
+
+def test_readme_style_usage_on_cpu():
+    """The reference README's quick start: a model, a normal loop, a tiering manager attached in
+    simulation mode."""
+    import torch
+    import torch.nn as nn
+
+    from zenyx_b200.models import SimpleTransformer
+    from zenyx_b200.train import Trainer, TrainerConfig
+    from zenyx_b200.train.belayd_kv_cache_tiering import BeladyKVCacheTieringManager
+
+    torch.manual_seed(0)
+    model = SimpleTransformer(vocab_size=100, d_model=32, num_layers=2, nhead=4, dim_feedforward=64)
+    mgr = BeladyKVCacheTieringManager(num_devices=8, context_length=4096, num_layers=12)
+    assert mgr.simulate_mode and mgr.plan().hit_rate > 0.5
+    tr = Trainer(model, TrainerConfig(lr=1e-3))
+    x = torch.randint(0, 100, (4, 16))
+
+    class CE(nn.Module):
+        def forward(self, out, tgt):
+            return nn.functional.cross_entropy(out.reshape(-1, out.shape[-1]), tgt.reshape(-1))
+
+    losses = tr.fit([(x, x)] * 5, CE(), 5)
+    assert len(losses) == 5 and losses[-1] < losses[0]

@@ -1,0 +1,131 @@
+import pytest
+import torch
+import torch.nn as nn
+
+from zenyx_b200.memory import ActivationManager, CheckpointPolicy, MemoryTracker
+from zenyx_b200.runtime import (ExecutionGraph, ExecutionGraphBuilder, ExecutionPlan, OpNode, OpType, Scheduler,
+                                TopologyConfig, validate_graph)
+
+
+def _mlp():
+    return nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+
+
+def test_graph_rejects_duplicates_unknowns_and_cycles():
+    g = ExecutionGraph()
+    g.add_node(OpNode("a", OpType.FORWARD))
+    g.add_node(OpNode("b", OpType.FORWARD))
+    g.add_node(OpNode("c", OpType.BACKWARD))
+    with pytest.raises(ValueError):
+        g.add_node(OpNode("a", OpType.FORWARD))
+    with pytest.raises(ValueError):
+        g.add_dependency("a", "zzz")
+    g.add_dependency("b", "a")
+    g.add_dependency("c", "b")
+    with pytest.raises(ValueError):
+        g.add_dependency("a", "c")
+    assert g.topological_order() == ["a", "b", "c"]
+    assert g.get_forward_execution_order() == ["a", "b"] and g.get_backward_execution_order() == ["c"]
+    assert g.validate()
+
+
+def test_builder_output_validates_and_executes():
+    model = _mlp()
+    g = ExecutionGraphBuilder().build_from_model(model, torch.randn(2, 8), world_size=2)
+    res = validate_graph(g)
+    assert res.is_valid, res.errors
+    s = g.summarize()
+    assert s["num_forward"] == 3 and s["num_backward"] == 3 and s["num_comm"] == 1 and s["total_params"] == 212
+    assert s["total_flops"] > 0
+    sched = Scheduler(enable_overlap=False)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    loss = model(torch.randn(2, 8)).pow(2).mean()
+    sched.backward(loss, model=model, optimizer=opt, execution_graph=g)   # single process: all-reduce is a no-op
+    assert sched.step_count == 1
+
+
+def test_validator_reports_deadlock_and_missing_tensor():
+    g = ExecutionGraph()
+    g.add_node(OpNode("x", OpType.FORWARD))
+    g.add_node(OpNode("y", OpType.FORWARD))
+    g.add_node(OpNode("ar", OpType.ALLREDUCE, metadata={"op": "bogus"}))
+    g.dependencies["x"].append("y")
+    g.dependents["y"].append("x")
+    g.dependencies["y"].append("x")
+    g.dependents["x"].append("y")
+    res = validate_graph(g)
+    assert not res.is_valid
+    assert any("deadlock" in e for e in res.errors)
+    assert any("metadata['tensor']" in e for e in res.errors)
+    assert any("unknown reduce op" in e for e in res.errors)
+
+
+def test_scheduler_priority_compute_then_intra_then_inter():
+    g = ExecutionGraph()
+    g.add_node(OpNode("inter", OpType.ALLREDUCE, device_ids=[0, 8], metadata={"tensor": torch.zeros(1)}))
+    g.add_node(OpNode("intra", OpType.ALLREDUCE, device_ids=[0, 1], metadata={"tensor": torch.zeros(1)}))
+    g.add_node(OpNode("comp", OpType.BACKWARD))
+    s = Scheduler(enable_overlap=False, topology=TopologyConfig(intra_node_ranks=[0, 1, 2, 3], inter_node_ranks=[0, 8]))
+    assert s._execute_graph_nodes(g) == ["comp", "intra", "inter"]
+
+
+def test_accumulation_steps_once_and_scales_like_a_big_batch():
+    torch.manual_seed(0)
+    m1, m2 = _mlp(), _mlp()
+    m2.load_state_dict(m1.state_dict())
+    x, y = torch.randn(8, 8), torch.randn(8, 4)
+    o1 = torch.optim.SGD(m1.parameters(), lr=0.1)
+    o2 = torch.optim.SGD(m2.parameters(), lr=0.1)
+    s = Scheduler(accumulation_steps=2, enable_overlap=False)
+    for i in range(2):
+        xb, yb = x[i * 4:(i + 1) * 4], y[i * 4:(i + 1) * 4]
+        s.backward(nn.functional.mse_loss(m1(xb), yb), model=m1, optimizer=o1)
+        assert s.step_count == i  # steps only at the boundary
+    nn.functional.mse_loss(m2(x), y).backward()
+    o2.step()
+    for a, b in zip(m1.parameters(), m2.parameters()):
+        assert torch.allclose(a, b, atol=1e-6)
+    assert s.get_stats()["step"] == 1 and s.accumulated_loss > 0
+
+
+def test_backward_accepts_quickstart_call_form():
+    m = _mlp()
+    opt = torch.optim.SGD(m.parameters(), lr=0.1)
+    before = [p.clone() for p in m.parameters()]
+    Scheduler(enable_overlap=False).backward(m(torch.randn(2, 8)).mean(), opt)
+    assert any(not torch.equal(a, b) for a, b in zip(before, m.parameters()))
+
+
+def test_activation_manager_selects_and_restores():
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.self_attn = nn.Linear(256, 256)
+            self.mlp = nn.Sequential(nn.Linear(256, 512), nn.ReLU(), nn.Linear(512, 256))
+
+        def forward(self, x):
+            return self.mlp(self.self_attn(x))
+
+    blk = Block()
+    mgr = ActivationManager(CheckpointPolicy(checkpoint_attention=False, checkpoint_ffn=True, min_trainable_params=1000))
+    assert mgr.hook_into_model(blk) == ["mlp"]
+    x = torch.randn(4, 256, requires_grad=True)
+    blk(x).sum().backward()
+    g1 = blk.mlp[0].weight.grad.clone()
+    mgr.unhook()
+    blk.zero_grad()
+    blk(x).sum().backward()
+    assert torch.allclose(g1, blk.mlp[0].weight.grad)
+    mgr.checkpoint_attention().checkpoint_ffn(False)
+    assert mgr.hook_into_model(blk) == ["self_attn"]
+    est = ActivationManager.estimate_memory_saving(12, 768, 512, 32)
+    assert abs(est["attention_mb"] - 301.99) < 1 and abs(est["total_gb"] - 1.51) < 0.01
+
+
+def test_memory_tracker_and_execution_plan():
+    t = MemoryTracker(history=4)
+    for _ in range(10):
+        t.snapshot()
+    assert len(t.snapshots) == 4 and not t.possible_leak()
+    p = ExecutionPlan.from_model(_mlp(), batch_size=2, seq_len=4)
+    assert p.num_forward_ops == 3 and p.estimate_memory_gb() > 0 and p.estimate_time_seconds() > 0
