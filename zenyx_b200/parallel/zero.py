@@ -26,13 +26,14 @@ from ..ops import _ext, fused
 class ZeroAdamW:
     def __init__(self, flat, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1,
                  max_grad_norm: Optional[float] = None, group=None, fused_peer: bool = True,
-                 barrier_timeout_ms: float = 60000.0):
+                 barrier_timeout_ms: float = 60000.0, single_process: bool = False):
         self.flat = flat
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        multi = dist.is_initialized() and not single_process   # single_process: ignore the process group
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
         assert flat.total % (4 * self.world) == 0, "flat buffer must split into 4-aligned shards"
         self.n_shard = flat.total // self.world
         self.shard_begin = self.rank * self.n_shard
