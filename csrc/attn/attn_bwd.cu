@@ -27,8 +27,10 @@ constexpr int HD = 128;
 constexpr int BT = 128;                    // tile edge in tokens (both Q and KV)
 constexpr int TILE_BYTES = BT * HD * 2;    // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk
-constexpr int NUM_THREADS = 192;           // 4 compute warps + TMA warp + MMA warp
-constexpr int DKDV_THREADS = 224;          // ... + peer-pull warp
+constexpr int NUM_THREADS = 320;           // 8 compute warps (two warpgroups) + TMA warp + MMA warp
+constexpr int DKDV_THREADS = 352;          // ... + peer-pull warp
+constexpr int W_TMA = 8, W_MMA = 9, W_PULL = 10;
+constexpr int N_COMPUTE = 256;             // compute threads
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -82,9 +84,6 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
-}
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 // K-major operand descriptor for k-step `k` (16 elements of d) of a [128 x 128] bf16 tile.
@@ -169,14 +168,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_ready, 128);
-    mbar_init(ds_ready, 128);
+    mbar_init(p_ready, N_COMPUTE);
+    mbar_init(ds_ready, N_COMPUTE);
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == W_MMA) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -191,10 +190,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (tile_allowed(p, q_tile_pos(p, t), kpos0)) ++n_items;
   n_items *= G;
 
-  if (warp == 6) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
+  if (warp == W_PULL) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
 
-  if (n_items > 0 && warp < 6) {
-    if (warp == 4) {
+  if (n_items > 0 && warp < W_PULL) {
+    if (warp == W_TMA) {
       // ------------------------------- TMA producer -------------------------------
       if (lane == 0) {
         tma_prefetch_desc(&tmQ);
@@ -230,7 +229,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
       }
-    } else if (warp == 5) {
+    } else if (warp == W_MMA) {
       // ------------------------------- MMA issuer ---------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);  // both operands K-major
@@ -259,7 +258,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (!mbar_wait(p_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts(t_dv, t_s + k * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
+          for (int k = 0; k < 8; ++k) umma_ts(t_dv, t_s + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
           if (has_next) {
             if (!mbar_wait(&qdo_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -271,7 +270,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (!mbar_wait(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts(t_dk, t_dp + k * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
+          for (int k = 0; k < 8; ++k) umma_ts(t_dk, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
           umma_commit(&qdo_empty[s]);
           if (has_next) {
 #pragma unroll
@@ -291,9 +290,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     } else {
       // ------------------------------- compute warps ------------------------------
-      const int r = warp * 32 + lane;  // KV row of this thread == TMEM lane
-      const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-      const uint32_t t_s = tmem_base + lane_base, t_dp = tmem_base + lane_base + 128;
+      // Two warpgroups: warpgroup wg owns query columns [64 wg, 64 wg + 64) of every KV row.
+      const int wg = warp >> 2;
+      const int lq = warp & 3;                 // TMEM lane quarter
+      const int r = lq * 32 + lane;            // KV row of this thread == TMEM lane
+      const int col0 = wg * 64;
+      const uint32_t lane_base = (uint32_t)(lq * 32) << 16;
+      const uint32_t t_s = tmem_base + lane_base + col0, t_dp = tmem_base + lane_base + 128 + col0;
       const int my_kpos = kpos0 + r;
       uint32_t n = 0;
       bool ok = true;
@@ -303,52 +306,48 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (!tile_allowed(p, qpos0, kpos0)) continue;
           const int s = n & 1;
           if (!wait_warp(&qdo_full[s], (n >> 1) & 1, abort_flag)) { ok = false; break; }
-          s_lse2[s * BT + r] = s_lse[s * BT + r] * LOG2E;
-          named_bar_sync(1, 128);
           if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          uint32_t sr[128];
+          uint32_t sr[64];
           tmem_ld_32x32b_x32(t_s + 0, sr);
           tmem_ld_32x32b_x32(t_s + 32, sr + 32);
-          tmem_ld_32x32b_x32(t_s + 64, sr + 64);
-          tmem_ld_32x32b_x32(t_s + 96, sr + 96);
           tmem_wait_ld();
           const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
-          const float* lse2 = s_lse2 + s * BT;
-          // column c is query qpos0 + c; it sees this key iff my_kpos <= qpos0 + c
+          const float* lse_nat = s_lse + s * BT + col0;   // natural-log LSE of the 64 queries of this half
+          // column c is query qpos0 + col0 + c; it sees this key iff my_kpos <= that position
+          const int qp = qpos0 + col0;
 #pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            float pv = fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lse2[c]));
-            if (diag && (my_kpos > qpos0 + c)) pv = 0.f;
+          for (int c = 0; c < 64; ++c) {
+            float pv = fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lse_nat[c] * LOG2E));
+            if (diag && (my_kpos > qp + c)) pv = 0.f;
             sr[c] = __float_as_uint(pv);
           }
           {
-            uint32_t pk[64];
+            // bf16 P^T for this half goes over the first 32 columns of the half this thread just read
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 64; ++c) pk[c] = pack_bf16x2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
-            tmem_st_32x32b_x32(t_s + 0, pk);
-            tmem_st_32x32b_x32(t_s + 32, pk + 32);
+            for (int c = 0; c < 32; ++c) pk[c] = pack_bf16x2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
+            tmem_st_32x32b_x32(t_s, pk);
           }
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(p_ready);
           if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const float* dl = s_delta + s * BT;
+          const float* dl = s_delta + s * BT + col0;
+          uint32_t dp[64];
+          tmem_ld_32x32b_x32(t_dp + 0, dp);
+          tmem_ld_32x32b_x32(t_dp + 32, dp + 32);
+          tmem_wait_ld();
+          {
+            uint32_t dsp[32];
 #pragma unroll
-          for (int ci = 0; ci < 4; ++ci) {
-            uint32_t dp[32];
-            tmem_ld_32x32b_x32(t_dp + ci * 32, dp);
-            tmem_wait_ld();
-            uint32_t dsp[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int c = ci * 32 + 2 * e;
-              const float d0 = __uint_as_float(sr[c]) * (__uint_as_float(dp[2 * e]) - dl[c]);
-              const float d1 = __uint_as_float(sr[c + 1]) * (__uint_as_float(dp[2 * e + 1]) - dl[c + 1]);
+            for (int e = 0; e < 32; ++e) {
+              const float d0 = __uint_as_float(sr[2 * e]) * (__uint_as_float(dp[2 * e]) - dl[2 * e]);
+              const float d1 = __uint_as_float(sr[2 * e + 1]) * (__uint_as_float(dp[2 * e + 1]) - dl[2 * e + 1]);
               dsp[e] = pack_bf16x2(d0, d1);
             }
-            tmem_st_32x32b_x16(t_dp + ci * 16, dsp);
+            tmem_st_32x32b_x32(t_dp, dsp);
           }
           tmem_wait_st();
           tc_fence_before();
@@ -356,17 +355,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           ++n;
         }
       }
-      // epilogue: add dV and scale * dK into the (possibly remote) fp32 accumulators
+      // epilogue: add dV and scale * dK into the (possibly remote) fp32 accumulators; each
+      // warpgroup drains its 64 columns of both accumulators
       if (ok) ok = wait_warp(acc_done, 0, abort_flag);
       tc_fence_after();
       if (ok) {
-        const size_t row_off = (((size_t)b * p.Skv + (size_t)j * BT + r) * p.Hkv + hk) * HD;
+        const size_t row_off = (((size_t)b * p.Skv + (size_t)j * BT + r) * p.Hkv + hk) * HD + col0;
         float* dv_row = p.dv + row_off;
         float* dk_row = p.dk + row_off;
 #pragma unroll
-        for (int ci = 0; ci < 4; ++ci) {
+        for (int ci = 0; ci < 2; ++ci) {
           uint32_t a[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_base + 256 + ci * 32, a);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + 256 + col0 + ci * 32, a);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 8; ++e)
@@ -374,9 +374,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                            __uint_as_float(a[4 * e + 2]), __uint_as_float(a[4 * e + 3]));
         }
 #pragma unroll
-        for (int ci = 0; ci < 4; ++ci) {
+        for (int ci = 0; ci < 2; ++ci) {
           uint32_t a[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_base + 384 + ci * 32, a);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + 384 + col0 + ci * 32, a);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 8; ++e)
@@ -391,7 +391,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == W_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -442,14 +442,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(s_read, 128);
-    mbar_init(ds_ready, 128);
+    mbar_init(s_read, N_COMPUTE);
+    mbar_init(ds_ready, N_COMPUTE);
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == W_MMA) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -463,7 +463,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (tile_allowed(p, qpos0, kv_tile_pos(p, j))) ++n_items;
 
   if (n_items > 0) {
-    if (warp == 4) {
+    if (warp == W_TMA) {
       if (lane == 0) {
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
@@ -492,7 +492,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-    } else if (warp == 5) {
+    } else if (warp == W_MMA) {
       if (lane == 0) {
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);
         constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);
@@ -527,7 +527,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (!mbar_wait(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts(t_dq, t_dp + k * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
+          for (int k = 0; k < 8; ++k) umma_ts(t_dq, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
           umma_commit(&kv_empty[s]);
           if (has_next) {
 #pragma unroll
@@ -546,9 +546,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     } else {
-      const int r = warp * 32 + lane;  // query row == TMEM lane
-      const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-      const uint32_t t_s = tmem_base + lane_base, t_dp = tmem_base + lane_base + 128;
+      // Two warpgroups: warpgroup wg owns key columns [64 wg, 64 wg + 64) of every query row.
+      const int wg = warp >> 2;
+      const int lq = warp & 3;
+      const int r = lq * 32 + lane;  // query row == TMEM lane
+      const int col0 = wg * 64;
+      const uint32_t lane_base = (uint32_t)(lq * 32) << 16;
+      const uint32_t t_s = tmem_base + lane_base + col0, t_dp = tmem_base + lane_base + 128 + col0;
       const size_t stat_idx = ((size_t)b * p.Hq + hq) * p.Sq + (size_t)t * BT + r;
       const float lse2 = p.lse[stat_idx] * LOG2E;
       const float dlt = p.delta[stat_idx];
@@ -560,37 +564,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!tile_allowed(p, qpos0, kpos0)) continue;
         if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        uint32_t sr[128];
+        uint32_t sr[64];
         tmem_ld_32x32b_x32(t_s + 0, sr);
         tmem_ld_32x32b_x32(t_s + 32, sr + 32);
-        tmem_ld_32x32b_x32(t_s + 64, sr + 64);
-        tmem_ld_32x32b_x32(t_s + 96, sr + 96);
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(s_read);
         const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
+        const int kp = kpos0 + col0;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
+        for (int c = 0; c < 64; ++c) {
           float pv = fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lse2));
-          if (diag && (kpos0 + c > my_qpos)) pv = 0.f;
+          if (diag && (kp + c > my_qpos)) pv = 0.f;
           sr[c] = __float_as_uint(pv);
         }
         if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        uint32_t dp[64];
+        tmem_ld_32x32b_x32(t_dp + 0, dp);
+        tmem_ld_32x32b_x32(t_dp + 32, dp + 32);
+        tmem_wait_ld();
+        {
+          uint32_t dsp[32];
 #pragma unroll
-        for (int ci = 0; ci < 4; ++ci) {
-          uint32_t dp[32];
-          tmem_ld_32x32b_x32(t_dp + ci * 32, dp);
-          tmem_wait_ld();
-          uint32_t dsp[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int c = ci * 32 + 2 * e;
-            const float d0 = __uint_as_float(sr[c]) * (__uint_as_float(dp[2 * e]) - dlt);
-            const float d1 = __uint_as_float(sr[c + 1]) * (__uint_as_float(dp[2 * e + 1]) - dlt);
+          for (int e = 0; e < 32; ++e) {
+            const float d0 = __uint_as_float(sr[2 * e]) * (__uint_as_float(dp[2 * e]) - dlt);
+            const float d1 = __uint_as_float(sr[2 * e + 1]) * (__uint_as_float(dp[2 * e + 1]) - dlt);
             dsp[e] = pack_bf16x2(d0, d1);
           }
-          tmem_st_32x32b_x16(t_dp + ci * 16, dsp);
+          tmem_st_32x32b_x32(t_dp, dsp);   // bf16 dS for this half, over the columns this thread just read
         }
         tmem_wait_st();
         tc_fence_before();
@@ -600,11 +602,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) ok = wait_warp(acc_done, 0, abort_flag);
       tc_fence_after();
       if (ok) {
-        float* dq_row = p.dq + (((size_t)b * p.Sq + (size_t)t * BT + r) * p.Hq + hq) * HD;
+        float* dq_row = p.dq + (((size_t)b * p.Sq + (size_t)t * BT + r) * p.Hq + hq) * HD + col0;
 #pragma unroll
-        for (int ci = 0; ci < 4; ++ci) {
+        for (int ci = 0; ci < 2; ++ci) {
           uint32_t a[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_base + 256 + ci * 32, a);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + 256 + col0 + ci * 32, a);
           tmem_wait_ld();
           float4* dst = reinterpret_cast<float4*>(dq_row + ci * 32);
 #pragma unroll
@@ -625,7 +627,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == W_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }

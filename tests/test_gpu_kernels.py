@@ -421,3 +421,27 @@ def test_attn_bwd_block_sparse(C):
     assert _rel_err(dv, dv_r) < 2e-2
     assert _rel_err(dk, dk_r) < 2e-2
     assert _rel_err(dq, dq_r) < 2e-2
+
+
+def test_peer_barrier_wait_is_bounded(C):
+    """A flag that nothing sets: the barrier kernel must give up within its limit, report the
+    timeout through the status word, and leave the context usable."""
+    import time
+
+    from zenyx_b200.ops import _ext
+
+    flags = C.peer_alloc(256)
+    try:
+        t0 = time.perf_counter()
+        # pretend to be rank 0 of 2 with both flag arrays in our own memory: slot 1 is never written
+        C.peer_barrier([flags, flags + 128], 0, 1, 200.0)
+        with pytest.raises(_ext.KernelError) as ei:
+            _ext.check_status()
+        assert "timed out" in str(ei.value) and "peer barrier" in str(ei.value)
+        assert time.perf_counter() - t0 < 5.0
+        _ext.check_status()                      # the word was cleared; the context still works
+        x = torch.ones(8, device="cuda")
+        assert x.sum().item() == 8.0
+    finally:
+        torch.cuda.synchronize()
+        C.peer_free(flags)

@@ -109,6 +109,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--no-attn", action="store_true")
+    ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--no-bwd", action="store_true")
     args = ap.parse_args(argv)
     shapes = [(8192, 8192, 8192, False, False)]
@@ -120,7 +121,7 @@ def main(argv=None):
             (32768, 4096, 6144, False, True),    # dgrad of QKV
             (28672, 4096, 32768, True, True),    # wgrad of gate|up
         ]
-    for M, N, K, at, bt in shapes:
+    for M, N, K, at, bt in ([] if args.no_gemm else shapes):
         print(json.dumps(bench_gemm(M, N, K, at, bt)), flush=True)
     if not args.no_attn:
         for S in ([8192] if args.quick else [8192, 32768]):
