@@ -86,14 +86,16 @@ __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, fl
                : "memory");
 }
 
-// K-major operand descriptor for k-step `k` (16 elements of d) of a [128 x 128] bf16 tile.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int k) {
-  return make_smem_desc_sw128(tile_addr + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
+// Base descriptors of a [128 x 128] bf16 tile (built once per tile address) ...
+__device__ __forceinline__ uint64_t base_kmajor(uint32_t tile_addr) { return make_smem_desc_sw128(tile_addr, 16, 1024); }
+__device__ __forceinline__ uint64_t base_mnmajor(uint32_t tile_addr) {
+  return make_smem_desc_sw128(tile_addr, HALF_BYTES, 1024);
 }
-// MN-major operand descriptor for k-step `k` (16 token rows) of the same tile read transposed.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int k) {
-  return make_smem_desc_sw128(tile_addr + k * 16 * 128, HALF_BYTES, 1024);
+// ... and their k-step variants: one add each. K-major: 16 elements of d; MN-major: 16 token rows.
+__device__ __forceinline__ uint64_t desc_kmajor(uint64_t base, int k) {
+  return desc_advance(base, (k >> 2) * HALF_BYTES + (k & 3) * 32);
 }
+__device__ __forceinline__ uint64_t desc_mnmajor(uint64_t base, int k) { return desc_advance(base, k * 16 * 128); }
 
 // ------------------------------------------------------------------------------------------
 // delta[b, h, s] = sum_d dO * O
@@ -235,25 +237,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);  // both operands K-major
         constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);  // A from TMEM, B MN-major
         const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
-        const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+        const uint64_t k_addr = base_kmajor(smem_u32(sK)), v_addr = base_kmajor(smem_u32(sV));
+        const uint64_t q_k0 = base_kmajor(smem_u32(sQ)), do_k0 = base_kmajor(smem_u32(sdO));
+        const uint64_t q_mn0 = base_mnmajor(smem_u32(sQ)), do_mn0 = base_mnmajor(smem_u32(sdO));
         bool ok = mbar_wait(kv_full, 0, abort_flag);
         ok = ok && mbar_wait(&qdo_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
-          const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(k_addr, k), desc_kmajor(q_addr, k), idesc_kk, k > 0);
+          for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(k_addr, k), desc_kmajor(q_k0, k), idesc_kk, k > 0);
           umma_commit(s_full);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_dp, desc_kmajor(v_addr, k), desc_kmajor(do_addr, k), idesc_kk, k > 0);
+          for (int k = 0; k < 8; ++k) umma_ss(t_dp, desc_kmajor(v_addr, k), desc_kmajor(do_k0, k), idesc_kk, k > 0);
           umma_commit(dp_full);
         }
         int n = 0;
         for (; n < n_items && ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
           const bool has_next = n + 1 < n_items;
-          const uint32_t q_addr = smem_u32(sQ + s * TILE_BYTES), do_addr = smem_u32(sdO + s * TILE_BYTES);
-          const uint32_t qn_addr = smem_u32(sQ + sn * TILE_BYTES), don_addr = smem_u32(sdO + sn * TILE_BYTES);
+          const uint64_t q_addr = desc_advance(q_mn0, (uint32_t)s * TILE_BYTES);     // read transposed
+          const uint64_t do_addr = desc_advance(do_mn0, (uint32_t)s * TILE_BYTES);   // read transposed
+          const uint64_t qn_addr = desc_advance(q_k0, (uint32_t)sn * TILE_BYTES);
+          const uint64_t don_addr = desc_advance(do_k0, (uint32_t)sn * TILE_BYTES);
           // dV += P^T dO
           if (!mbar_wait(p_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
@@ -497,25 +502,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);
         constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);
         const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
-        const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+        const uint64_t q_addr = base_kmajor(smem_u32(sQ)), do_addr = base_kmajor(smem_u32(sdO));
+        const uint64_t k_k0 = base_kmajor(smem_u32(sK)), v_k0 = base_kmajor(smem_u32(sV));
+        const uint64_t k_mn0 = base_mnmajor(smem_u32(sK));
         bool ok = mbar_wait(qdo_full, 0, abort_flag);
         ok = ok && mbar_wait(&kv_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
-          const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(q_addr, k), desc_kmajor(k_addr, k), idesc_kk, k > 0);
+          for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(q_addr, k), desc_kmajor(k_k0, k), idesc_kk, k > 0);
           umma_commit(s_full);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_dp, desc_kmajor(do_addr, k), desc_kmajor(v_addr, k), idesc_kk, k > 0);
+          for (int k = 0; k < 8; ++k) umma_ss(t_dp, desc_kmajor(do_addr, k), desc_kmajor(v_k0, k), idesc_kk, k > 0);
           umma_commit(dp_full);
         }
         int n = 0;
         for (; n < n_items && ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
           const bool has_next = n + 1 < n_items;
-          const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
-          const uint32_t kn_addr = smem_u32(sK + sn * TILE_BYTES), vn_addr = smem_u32(sV + sn * TILE_BYTES);
+          const uint64_t k_addr = desc_advance(k_mn0, (uint32_t)s * TILE_BYTES);   // read transposed
+          const uint64_t kn_addr = desc_advance(k_k0, (uint32_t)sn * TILE_BYTES);
+          const uint64_t vn_addr = desc_advance(v_k0, (uint32_t)sn * TILE_BYTES);
           if (has_next) {
             if (!mbar_wait(s_read, n & 1, abort_flag)) { ok = false; break; }
             if (!mbar_wait(&kv_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }

@@ -178,6 +178,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(BQ, BKV, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(BQ, HD, 1, 1, 0, 1);
+      // Base descriptors are built once; every MMA below only adds a constant to them.
+      const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);          // K-major tiles
+      const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sV), HALF_BYTES, 1024);  // read transposed (MN-major)
       bool ok = mbar_wait(q_full, 0, abort_flag);
       tc_fence_after();
       uint32_t n = 0;
@@ -190,13 +194,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&p_ready[i], (cnt[i] - 1) & 1, abort_flag)) return false;
         if (!mbar_wait(&v_full[pend_stage[i]], pend_phase[i], abort_flag)) return false;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + pend_stage[i] * TILE_BYTES);
+        const uint64_t v_desc = desc_advance(v_desc0, (uint32_t)pend_stage[i] * TILE_BYTES);
         const uint32_t o_tmem = tmem_base + 256 + i * 128;
         const uint32_t p_tmem = tmem_base + i * 128;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          const uint64_t vdesc = make_smem_desc_sw128(v_addr + k * 16 * 128, HALF_BYTES, 1024);
-          umma_ts(o_tmem, p_tmem + k * 8, vdesc, idesc_pv, (cnt[i] > 1 || k > 0) ? 1u : 0u);
+          umma_ts(o_tmem, p_tmem + k * 8, desc_advance(v_desc, k * 16 * 128), idesc_pv,
+                  (cnt[i] > 1 || k > 0) ? 1u : 0u);
         }
         umma_commit(&o_done[i]);
         pend_stage[i] = -1;
@@ -220,13 +224,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_fence_after();
             k_waited = true;
           }
-          const uint32_t q_addr = smem_u32(sQ + i * TILE_BYTES);
-          const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
+          const uint64_t q_desc = desc_advance(q_desc0, (uint32_t)i * TILE_BYTES);
+          const uint64_t k_desc = desc_advance(k_desc0, (uint32_t)s * TILE_BYTES);
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
             const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-            umma_ss(tmem_base + i * 128, make_smem_desc_sw128(q_addr + off, 16, 1024),
-                    make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+            umma_ss(tmem_base + i * 128, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk,
+                    k > 0 ? 1u : 0u);
           }
           umma_commit(&s_full[i]);
           pend_stage[i] = s;
@@ -281,19 +285,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(s_tmem + 96, sr + 96);
         tmem_wait_ld();
         const bool diag = p.causal && (kpos0 + BKV - 1 > qpos[i]);
-        float mx = NEG_BIG;
+        // four independent running maxima / sums instead of one dependent chain of 128 operations
+        float mx4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};
         if (diag) {
 #pragma unroll
           for (int c = 0; c < 128; ++c) {
             float v = __uint_as_float(sr[c]);
             v = (kpos0 + c > my_qpos) ? NEG_BIG : v;
             sr[c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            mx4[c & 3] = fmaxf(mx4[c & 3], v);
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+          for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
         }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_cur = mx * p.scale_log2;
         if (cnt == 0) {
           m_used = m_cur;
@@ -319,15 +325,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
         uint32_t pk[64];
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), p.scale_log2, -m_used));
           const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), p.scale_log2, -m_used));
-          sum += p0 + p1;
+          sum4[c & 3] += p0 + p1;
           pk[c] = pack_bf16x2(p0, p1);
         }
-        l += sum;
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tmem_st_32x32b_x32(s_tmem + 0, pk);
         tmem_st_32x32b_x32(s_tmem + 32, pk + 32);
         tmem_wait_st();

@@ -260,6 +260,16 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       : "memory");
 }
 
+// Register re-balancing between warpgroups (all four warps of a warpgroup must execute it).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ----------------------------------------------------------------------------------------------
 // Descriptors
 // ----------------------------------------------------------------------------------------------
@@ -277,6 +287,10 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   d |= (uint64_t)2 << 61;  // SWIZZLE_128B
   return d;
 }
+
+// Byte offset applied to a descriptor's start-address field (the field holds address >> 4 and the
+// tiles used here never carry out of it), so per-k-step descriptors cost one add.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 
 // Instruction descriptor for kind::f16 (fmt: 0 = fp16, 1 = bf16) / kind::f8f6f4 (fmt: 0 = e4m3, 1 = e5m2)
 // with fp32 accumulation. a_mn / b_mn: 1 when that operand is MN-major in shared memory.

@@ -141,6 +141,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------- MMA issuer ---------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // stage-0 descriptors; stages and k-steps are reached by adding constants
+      const uint64_t a_desc0 = A_MN ? make_smem_desc_sw128(smem_u32(sA), CHUNK_BYTES, 1024)
+                                    : make_smem_desc_sw128(smem_u32(sA), 16, 1024);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem_u32(sB), CHUNK_BYTES, 1024)
+                                    : make_smem_desc_sw128(smem_u32(sB), 16, 1024);
       uint32_t it = 0;
       uint32_t lt = 0;  // local tile counter
       bool ok = true;
@@ -153,14 +158,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int s = it % STAGES;
           if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+          const uint64_t a_base = desc_advance(a_desc0, (uint32_t)s * A_STAGE_BYTES);
+          const uint64_t b_base = desc_advance(b_desc0, (uint32_t)s * B_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = A_MN ? make_smem_desc_sw128(a_addr + k * UMMA_K * 128, CHUNK_BYTES, 1024)
-                                         : make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
-            const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_addr + k * UMMA_K * 128, CHUNK_BYTES, 1024)
-                                         : make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
+            const uint64_t a_desc = desc_advance(a_base, A_MN ? k * UMMA_K * 128 : k * UMMA_K * 2);
+            const uint64_t b_desc = desc_advance(b_base, B_MN ? k * UMMA_K * 128 : k * UMMA_K * 2);
             umma_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // stage is free once these MMAs have read it
