@@ -233,23 +233,23 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     } else if (warp == W_MMA) {
       // ------------------------------- MMA issuer ---------------------------------
-      if (lane == 0) {
+      {  // all 32 lanes run this loop; the instructions themselves are issued by one elected lane
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);  // both operands K-major
         constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);  // A from TMEM, B MN-major
         const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
         const uint64_t k_addr = base_kmajor(smem_u32(sK)), v_addr = base_kmajor(smem_u32(sV));
         const uint64_t q_k0 = base_kmajor(smem_u32(sQ)), do_k0 = base_kmajor(smem_u32(sdO));
         const uint64_t q_mn0 = base_mnmajor(smem_u32(sQ)), do_mn0 = base_mnmajor(smem_u32(sdO));
-        bool ok = mbar_wait(kv_full, 0, abort_flag);
-        ok = ok && mbar_wait(&qdo_full[0], 0, abort_flag);
+        bool ok = mbar_wait_w(kv_full, 0, abort_flag);
+        ok = ok && mbar_wait_w(&qdo_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(k_addr, k), desc_kmajor(q_k0, k), idesc_kk, k > 0);
-          umma_commit(s_full);
+          for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(k_addr, k), desc_kmajor(q_k0, k), idesc_kk, k > 0);
+          umma_commit_w(s_full);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_dp, desc_kmajor(v_addr, k), desc_kmajor(do_k0, k), idesc_kk, k > 0);
-          umma_commit(dp_full);
+          for (int k = 0; k < 8; ++k) umma_ss_w(t_dp, desc_kmajor(v_addr, k), desc_kmajor(do_k0, k), idesc_kk, k > 0);
+          umma_commit_w(dp_full);
         }
         int n = 0;
         for (; n < n_items && ok; ++n) {
@@ -260,34 +260,34 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const uint64_t qn_addr = desc_advance(q_k0, (uint32_t)sn * TILE_BYTES);
           const uint64_t don_addr = desc_advance(do_k0, (uint32_t)sn * TILE_BYTES);
           // dV += P^T dO
-          if (!mbar_wait(p_ready, n & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_w(p_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts(t_dv, t_s + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
+          for (int k = 0; k < 8; ++k) umma_ts_w(t_dv, t_s + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
           if (has_next) {
-            if (!mbar_wait(&qdo_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_w(&qdo_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(k_addr, k), desc_kmajor(qn_addr, k), idesc_kk, k > 0);
-            umma_commit(s_full);
+            for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(k_addr, k), desc_kmajor(qn_addr, k), idesc_kk, k > 0);
+            umma_commit_w(s_full);
           }
           // dK += dS^T Q
-          if (!mbar_wait(ds_ready, n & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts(t_dk, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
-          umma_commit(&qdo_empty[s]);
+          for (int k = 0; k < 8; ++k) umma_ts_w(t_dk, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_commit_w(&qdo_empty[s]);
           if (has_next) {
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-              umma_ss(t_dp, desc_kmajor(v_addr, k), desc_kmajor(don_addr, k), idesc_kk, k > 0);
-            umma_commit(dp_full);
+              umma_ss_w(t_dp, desc_kmajor(v_addr, k), desc_kmajor(don_addr, k), idesc_kk, k > 0);
+            umma_commit_w(dp_full);
           }
         }
-        if (ok) umma_commit(acc_done);
+        if (ok) umma_commit_w(acc_done);
         if (!ok) {
-          report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
-          umma_commit(drain_bar);
+          if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
+          umma_commit_w(drain_bar);
           const uint64_t t0 = globaltimer_ns();
           while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {
           }
@@ -498,23 +498,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     } else if (warp == W_MMA) {
-      if (lane == 0) {
+      {  // all 32 lanes run this loop; the instructions themselves are issued by one elected lane
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);
         constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);
         const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
         const uint64_t q_addr = base_kmajor(smem_u32(sQ)), do_addr = base_kmajor(smem_u32(sdO));
         const uint64_t k_k0 = base_kmajor(smem_u32(sK)), v_k0 = base_kmajor(smem_u32(sV));
         const uint64_t k_mn0 = base_mnmajor(smem_u32(sK));
-        bool ok = mbar_wait(qdo_full, 0, abort_flag);
-        ok = ok && mbar_wait(&kv_full[0], 0, abort_flag);
+        bool ok = mbar_wait_w(qdo_full, 0, abort_flag);
+        ok = ok && mbar_wait_w(&kv_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(q_addr, k), desc_kmajor(k_k0, k), idesc_kk, k > 0);
-          umma_commit(s_full);
+          for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(q_addr, k), desc_kmajor(k_k0, k), idesc_kk, k > 0);
+          umma_commit_w(s_full);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss(t_dp, desc_kmajor(do_addr, k), desc_kmajor(v_k0, k), idesc_kk, k > 0);
-          umma_commit(dp_full);
+          for (int k = 0; k < 8; ++k) umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(v_k0, k), idesc_kk, k > 0);
+          umma_commit_w(dp_full);
         }
         int n = 0;
         for (; n < n_items && ok; ++n) {
@@ -524,29 +524,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const uint64_t kn_addr = desc_advance(k_k0, (uint32_t)sn * TILE_BYTES);
           const uint64_t vn_addr = desc_advance(v_k0, (uint32_t)sn * TILE_BYTES);
           if (has_next) {
-            if (!mbar_wait(s_read, n & 1, abort_flag)) { ok = false; break; }
-            if (!mbar_wait(&kv_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_w(s_read, n & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_w(&kv_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < 8; ++k) umma_ss(t_s, desc_kmajor(q_addr, k), desc_kmajor(kn_addr, k), idesc_kk, k > 0);
-            umma_commit(s_full);
+            for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(q_addr, k), desc_kmajor(kn_addr, k), idesc_kk, k > 0);
+            umma_commit_w(s_full);
           }
-          if (!mbar_wait(ds_ready, n & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts(t_dq, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
-          umma_commit(&kv_empty[s]);
+          for (int k = 0; k < 8; ++k) umma_ts_w(t_dq, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_commit_w(&kv_empty[s]);
           if (has_next) {
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-              umma_ss(t_dp, desc_kmajor(do_addr, k), desc_kmajor(vn_addr, k), idesc_kk, k > 0);
-            umma_commit(dp_full);
+              umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(vn_addr, k), idesc_kk, k > 0);
+            umma_commit_w(dp_full);
           }
         }
-        if (ok) umma_commit(acc_done);
+        if (ok) umma_commit_w(acc_done);
         if (!ok) {
-          report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
-          umma_commit(drain_bar);
+          if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
+          umma_commit_w(drain_bar);
           const uint64_t t0 = globaltimer_ns();
           while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {
           }

@@ -175,14 +175,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer ---------------------------------
-    if (lane == 0) {
+    {  // all 32 lanes run this loop; the instructions themselves are issued by one elected lane
       constexpr uint32_t idesc_qk = make_idesc(BQ, BKV, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(BQ, HD, 1, 1, 0, 1);
       // Base descriptors are built once; every MMA below only adds a constant to them.
       const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);          // K-major tiles
       const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sV), HALF_BYTES, 1024);  // read transposed (MN-major)
-      bool ok = mbar_wait(q_full, 0, abort_flag);
+      bool ok = mbar_wait_w(q_full, 0, abort_flag);
       tc_fence_after();
       uint32_t n = 0;
       int pend_stage[2] = {-1, -1};
@@ -191,18 +191,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       int prev_stage = -1;
 
       auto issue_pv = [&](int i) -> bool {
-        if (!mbar_wait(&p_ready[i], (cnt[i] - 1) & 1, abort_flag)) return false;
-        if (!mbar_wait(&v_full[pend_stage[i]], pend_phase[i], abort_flag)) return false;
+        if (!mbar_wait_w(&p_ready[i], (cnt[i] - 1) & 1, abort_flag)) return false;
+        if (!mbar_wait_w(&v_full[pend_stage[i]], pend_phase[i], abort_flag)) return false;
         tc_fence_after();
         const uint64_t v_desc = desc_advance(v_desc0, (uint32_t)pend_stage[i] * TILE_BYTES);
         const uint32_t o_tmem = tmem_base + 256 + i * 128;
         const uint32_t p_tmem = tmem_base + i * 128;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          umma_ts(o_tmem, p_tmem + k * 8, desc_advance(v_desc, k * 16 * 128), idesc_pv,
+          umma_ts_w(o_tmem, p_tmem + k * 8, desc_advance(v_desc, k * 16 * 128), idesc_pv,
                   (cnt[i] > 1 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&o_done[i]);
+        umma_commit_w(&o_done[i]);
         pend_stage[i] = -1;
         return true;
       };
@@ -220,7 +220,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           if (!need[i]) continue;
           if (!k_waited) {
-            if (!mbar_wait(&k_full[s], ph, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_w(&k_full[s], ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             k_waited = true;
           }
@@ -229,17 +229,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
             const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-            umma_ss(tmem_base + i * 128, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk,
+            umma_ss_w(tmem_base + i * 128, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk,
                     k > 0 ? 1u : 0u);
           }
-          umma_commit(&s_full[i]);
+          umma_commit_w(&s_full[i]);
           pend_stage[i] = s;
           pend_phase[i] = ph;
           ++cnt[i];
         }
         if (!ok) break;
-        umma_commit(&k_empty[s]);
-        if (prev_stage >= 0) umma_commit(&v_empty[prev_stage]);
+        umma_commit_w(&k_empty[s]);
+        if (prev_stage >= 0) umma_commit_w(&v_empty[prev_stage]);
         prev_stage = s;
         ++n;
       }
@@ -249,8 +249,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       if (!ok) {
-        report(p.status, ZX_ERR_TIMEOUT, /*site=*/12, (int)n);
-        umma_commit(drain_bar);
+        if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/12, (int)n);
+        umma_commit_w(drain_bar);
         const uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {
         }

@@ -139,7 +139,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------
-    if (lane == 0) {
+    {  // all 32 lanes run this loop; the instructions themselves are issued by one elected lane
       constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       // stage-0 descriptors; stages and k-steps are reached by adding constants
       const uint64_t a_desc0 = A_MN ? make_smem_desc_sw128(smem_u32(sA), CHUNK_BYTES, 1024)
@@ -151,12 +151,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
         const uint32_t buf = lt & 1;
-        if (!mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_w(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_w(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint64_t a_base = desc_advance(a_desc0, (uint32_t)s * A_STAGE_BYTES);
           const uint64_t b_base = desc_advance(b_desc0, (uint32_t)s * B_STAGE_BYTES);
@@ -164,15 +164,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t a_desc = desc_advance(a_base, A_MN ? k * UMMA_K * 128 : k * UMMA_K * 2);
             const uint64_t b_desc = desc_advance(b_base, B_MN ? k * UMMA_K * 128 : k * UMMA_K * 2);
-            umma_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_ss_w(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty[s]);  // stage is free once these MMAs have read it
+          umma_commit_w(&empty[s]);  // stage is free once these MMAs have read it
         }
-        if (ok) umma_commit(&acc_full[buf]);
+        if (ok) umma_commit_w(&acc_full[buf]);
       }
       if (!ok) {
-        report(p.status, ZX_ERR_TIMEOUT, /*site=*/2, (int)it);
-        umma_commit(drain_bar);
+        if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/2, (int)it);
+        umma_commit_w(drain_bar);
         uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {
         }
