@@ -71,6 +71,9 @@ struct AttnBwdArgs {
   AttnLayout q_layout, kv_layout;
   int compute_delta = 1;  // run the delta pre-pass (once per backward; later ring steps reuse it)
   int dq_accumulate = 0;  // add to the dq already present instead of overwriting it (ring step > 0)
+  // Optional in-kernel timeline of the dQ kernel's first CTA: 64 iterations x 16 slots of SM clock
+  // stamps (slots 0-5: compute thread 0 after each phase, 8-10: MMA warp). Null: no tracing.
+  long long* trace = nullptr;
   const void* pull_src = nullptr;  // same fused peer pull as in the forward (done by the dK/dV kernel)
   void* pull_dst = nullptr;
   size_t pull_bytes = 0;

@@ -51,8 +51,15 @@ struct BwdParams {
   const uint4* pull_src;
   uint4* pull_dst;
   size_t pull_nvec;
+  long long* trace;
   Status* status;
 };
+
+// clock stamp of one pipeline event (dQ kernel, first CTA only, when a trace buffer is given)
+#define ZX_TRACE(iter, slot)                                                          \
+  do {                                                                                \
+    if (p.trace != nullptr && blockIdx.x == 0 && (iter) < 64) p.trace[(iter) * 16 + (slot)] = clock64(); \
+  } while (0)
 
 __device__ __forceinline__ bool tile_allowed(const BwdParams& p, int qpos0, int kpos0) {
   if (p.causal && kpos0 > qpos0) return false;
@@ -318,14 +325,22 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tmem_ld_32x32b_x32(t_s + 32, sr + 32);
           tmem_wait_ld();
           const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
-          const float* lse_nat = s_lse + s * BT + col0;   // natural-log LSE of the 64 queries of this half
-          // column c is query qpos0 + col0 + c; it sees this key iff my_kpos <= that position
-          const int qp = qpos0 + col0;
+          // packed fp32x2 math: two query columns per instruction
+          const float2* lse_nat2 = reinterpret_cast<const float2*>(s_lse + s * BT + col0);
+          const int qp = qpos0 + col0;   // column c is query qp + c; it sees this key iff my_kpos <= qp + c
+          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
+          const float2 nlog2e = make_float2(-LOG2E, -LOG2E);
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            float pv = fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lse_nat[c] * LOG2E));
-            if (diag && (my_kpos > qp + c)) pv = 0.f;
-            sr[c] = __float_as_uint(pv);
+          for (int c = 0; c < 32; ++c) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2,
+                                        __fmul2_rn(lse_nat2[c], nlog2e));
+            float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
+            if (diag) {
+              if (my_kpos > qp + 2 * c) p0 = 0.f;
+              if (my_kpos > qp + 2 * c + 1) p1 = 0.f;
+            }
+            sr[2 * c] = __float_as_uint(p0);
+            sr[2 * c + 1] = __float_as_uint(p1);
           }
           {
             // bf16 P^T for this half goes over the first 32 columns of the half this thread just read
@@ -339,7 +354,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           mbar_arrive(p_ready);
           if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const float* dl = s_delta + s * BT + col0;
+          const float2* dl2 = reinterpret_cast<const float2*>(s_delta + s * BT + col0);
           uint32_t dp[64];
           tmem_ld_32x32b_x32(t_dp + 0, dp);
           tmem_ld_32x32b_x32(t_dp + 32, dp + 32);
@@ -348,9 +363,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             uint32_t dsp[32];
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              const float d0 = __uint_as_float(sr[2 * e]) * (__uint_as_float(dp[2 * e]) - dl[2 * e]);
-              const float d1 = __uint_as_float(sr[2 * e + 1]) * (__uint_as_float(dp[2 * e + 1]) - dl[2 * e + 1]);
-              dsp[e] = pack_bf16x2(d0, d1);
+              const float2 dl = dl2[e];
+              const float2 t2 = __fadd2_rn(make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])),
+                                           make_float2(-dl.x, -dl.y));
+              const float2 d = __fmul2_rn(make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), t2);
+              dsp[e] = pack_bf16x2(d.x, d.y);
             }
             tmem_st_32x32b_x32(t_dp, dsp);
           }
@@ -533,15 +550,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
           if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
+          if (lane == 0) ZX_TRACE(n, 8);
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_ts_w(t_dq, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
           umma_commit_w(&kv_empty[s]);
+          if (lane == 0) ZX_TRACE(n, 9);
           if (has_next) {
 #pragma unroll
             for (int k = 0; k < 8; ++k)
               umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(vn_addr, k), idesc_kk, k > 0);
             umma_commit_w(dp_full);
           }
+          if (lane == 0) ZX_TRACE(n, 10);
         }
         if (ok) umma_commit_w(acc_done);
         if (!ok) {
@@ -571,37 +591,56 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!tile_allowed(p, qpos0, kpos0)) continue;
         if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (threadIdx.x == 0) ZX_TRACE(n, 0);
+        if (threadIdx.x == 160) ZX_TRACE(n, 11);
         uint32_t sr[64];
         tmem_ld_32x32b_x32(t_s + 0, sr);
         tmem_ld_32x32b_x32(t_s + 32, sr + 32);
         tmem_wait_ld();
+        if (threadIdx.x == 0) ZX_TRACE(n, 1);
         tc_fence_before();
         mbar_arrive(s_read);
         const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
         const int kp = kpos0 + col0;
+        const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 nl2 = make_float2(-lse2, -lse2);
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float pv = fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lse2));
-          if (diag && (kp + c > my_qpos)) pv = 0.f;
-          sr[c] = __float_as_uint(pv);
+        for (int c = 0; c < 32; ++c) {   // packed fp32x2 math: two key columns per instruction
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2, nl2);
+          float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
+          if (diag) {
+            if (kp + 2 * c > my_qpos) p0 = 0.f;
+            if (kp + 2 * c + 1 > my_qpos) p1 = 0.f;
+          }
+          sr[2 * c] = __float_as_uint(p0);
+          sr[2 * c + 1] = __float_as_uint(p1);
         }
+        if (threadIdx.x == 0) ZX_TRACE(n, 2);
+        if (threadIdx.x == 160) ZX_TRACE(n, 12);
         if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (threadIdx.x == 0) ZX_TRACE(n, 3);
         uint32_t dp[64];
         tmem_ld_32x32b_x32(t_dp + 0, dp);
         tmem_ld_32x32b_x32(t_dp + 32, dp + 32);
         tmem_wait_ld();
+        if (threadIdx.x == 0) ZX_TRACE(n, 4);
         {
           uint32_t dsp[32];
 #pragma unroll
+          const float2 ndl = make_float2(-dlt, -dlt);
+#pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const float d0 = __uint_as_float(sr[2 * e]) * (__uint_as_float(dp[2 * e]) - dlt);
-            const float d1 = __uint_as_float(sr[2 * e + 1]) * (__uint_as_float(dp[2 * e + 1]) - dlt);
-            dsp[e] = pack_bf16x2(d0, d1);
+            const float2 t2 = __fadd2_rn(make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), ndl);
+            const float2 d = __fmul2_rn(make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), t2);
+            dsp[e] = pack_bf16x2(d.x, d.y);
           }
+          if (threadIdx.x == 0) ZX_TRACE(n, 6);
           tmem_st_32x32b_x32(t_dp, dsp);   // bf16 dS for this half, over the columns this thread just read
         }
         tmem_wait_st();
+        if (threadIdx.x == 0) ZX_TRACE(n, 5);
+        if (threadIdx.x == 160) ZX_TRACE(n, 13);
         tc_fence_before();
         mbar_arrive(ds_ready);
         ++n;
@@ -689,6 +728,7 @@ void launch_attn_bwd(const AttnBwdArgs& a) {
   p.pull_src = (const uint4*)a.pull_src;
   p.pull_dst = (uint4*)a.pull_dst;
   p.pull_nvec = a.pull_src != nullptr ? a.pull_bytes / 16 : 0;
+  p.trace = a.trace;
   p.status = a.status;
   static bool configured = false;
   if (!configured) {

@@ -327,9 +327,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t pk[64];
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), p.scale_log2, -m_used));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), p.scale_log2, -m_used));
+        const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 nm2 = make_float2(-m_used, -m_used);
+        for (int c = 0; c < 64; ++c) {   // packed fp32x2 FMA: two columns per instruction
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2, nm2);
+          const float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
           sum4[c & 3] += p0 + p1;
           pk[c] = pack_bf16x2(p0, p1);
         }

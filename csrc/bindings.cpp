@@ -158,7 +158,8 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
               Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, int64_t window_blocks,
               int64_t global_every, const std::vector<int64_t>& q_chunk_pos, const std::vector<int64_t>& kv_chunk_pos,
-              bool compute_delta, bool dq_accumulate, int64_t pull_src, int64_t pull_dst, int64_t pull_bytes) {
+              bool compute_delta, bool dq_accumulate, int64_t pull_src, int64_t pull_dst, int64_t pull_bytes,
+              const c10::optional<Tensor>& trace) {
   check_qkv(q, "q");
   check_qkv(k, "k");
   check_qkv(v, "v");
@@ -187,6 +188,10 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.pull_src = reinterpret_cast<const void*>(pull_src);
   a.pull_dst = reinterpret_cast<void*>(pull_dst);
   a.pull_bytes = (size_t)pull_bytes;
+  if (trace.has_value()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 64 * 16, "trace: int64[1024]");
+    a.trace = reinterpret_cast<long long*>(trace->data_ptr());
+  }
   a.status = status_ptr();
   a.stream = cur_stream();
   zx::launch_attn_bwd(a);
@@ -471,7 +476,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("read_status", &read_status, "read (and optionally clear) the kernel status word");
   m.def("gemm", &gemm);
   m.def("attn_fwd", &attn_fwd);
-  m.def("attn_bwd", &attn_bwd);
+  m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("d_o"), py::arg("lse"),
+        py::arg("delta"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("scale"), py::arg("causal"),
+        py::arg("window_blocks"), py::arg("global_every"), py::arg("q_chunk_pos"), py::arg("kv_chunk_pos"),
+        py::arg("compute_delta"), py::arg("dq_accumulate"), py::arg("pull_src"), py::arg("pull_dst"),
+        py::arg("pull_bytes"), py::arg("trace") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope_qkv", &rope_qkv);
