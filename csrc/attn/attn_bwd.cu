@@ -28,7 +28,6 @@ constexpr int BT = 128;                    // tile edge in tokens (both Q and KV
 constexpr int TILE_BYTES = BT * HD * 2;    // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk
 constexpr int NUM_THREADS = 320;           // 8 compute warps (two warpgroups) + TMA warp + MMA warp
-constexpr int DKDV_THREADS = 352;          // ... + peer-pull warp
 constexpr int W_TMA = 8, W_MMA = 9, W_PULL = 10;
 constexpr int N_COMPUTE = 256;             // compute threads
 constexpr int TMEM_COLS = 512;
@@ -56,6 +55,15 @@ struct BwdParams {
 };
 
 // clock stamp of one pipeline event (dQ kernel, first CTA only, when a trace buffer is given)
+#define ZX_TRACE_DKDV(iter, slot)                                                     \
+  do {                                                                                \
+    if (p.trace != nullptr && blockIdx.x == 0 && (iter) < 64) p.trace[1024 + (iter) * 16 + (slot)] = clock64(); \
+  } while (0)
+#define ZX_TRACE_W(iter, k)                                                           \
+  do {                                                                                \
+    if (p.trace != nullptr && blockIdx.x == 0 && lane == 0 && warp < 8 && (iter) >= 8 && (iter) < 24)                      \
+      p.trace[2048 + (((iter) - 8) * 8 + warp) * 8 + (k)] = clock64();                                          \
+  } while (0)
 #define ZX_TRACE(iter, slot)                                                          \
   do {                                                                                \
     if (p.trace != nullptr && blockIdx.x == 0 && (iter) < 64) p.trace[(iter) * 16 + (slot)] = clock64(); \
@@ -82,12 +90,7 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volati
   const bool ok = mbar_wait(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
 }
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
+
 __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
@@ -131,8 +134,22 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 // ------------------------------------------------------------------------------------------
 // dK / dV
 // ------------------------------------------------------------------------------------------
-constexpr int DKDV_SMEM = 2 * TILE_BYTES /*K,V*/ + 4 * TILE_BYTES /*Q,dO x2*/ + 3 * 2 * BT * 4 /*lse,delta,lse2*/ +
-                          1024 + 256;
+// Q lives until dK of its item has been issued, dO only until dV: a 3-deep Q ring and a 2-deep dO
+// ring free every slot a full iteration before its next tile is needed, which hides the TMA latency.
+constexpr int Q_STAGES = 3, DO_STAGES = 2;
+// Sixteen compute warps: four column groups of 32 queries times the four TMEM lane quarters. The
+// exponential phase is bound by the special-function unit whatever the warp count; everything
+// around it (TMEM round trips, barrier latency, the dS arithmetic) is per-warp serial time, and
+// four warps per scheduler overlap it where two could not.
+constexpr int KW_COMPUTE = 16, KW_TMA = 16, KW_MMA = 17, KW_PULL = 18;
+constexpr int KN_COMPUTE = KW_COMPUTE * 32;
+constexpr int DKDV_THREADS = (KW_COMPUTE + 3) * 32;
+// Tail of the dK/dV kernel's shared memory: alignment slack, barriers, and two buffers of 256
+// per-query statistics (-lse * log2e for 128 queries, then -delta for the same 128).
+constexpr int DKDV_ALIGN_SLACK = 768, DKDV_BAR_BYTES = 192, DKDV_STAT_BYTES = 2 * 256 * 4;
+constexpr int DKDV_SMEM =
+    2 * TILE_BYTES /*K,V*/ + (Q_STAGES + DO_STAGES) * TILE_BYTES + DKDV_ALIGN_SLACK + DKDV_BAR_BYTES + DKDV_STAT_BYTES;
+static_assert(DKDV_SMEM <= 227 * 1024, "dK/dV kernel shared memory");
 
 __global__ void __launch_bounds__(DKDV_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
@@ -141,23 +158,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + TILE_BYTES;
-  uint8_t* sQ = smem + 2 * TILE_BYTES;   // [2]
-  uint8_t* sdO = smem + 4 * TILE_BYTES;  // [2]
-  float* s_lse = reinterpret_cast<float*>(smem + 6 * TILE_BYTES);  // [2][128] written by TMA
-  float* s_delta = s_lse + 2 * BT;                                 // [2][128] written by TMA
-  float* s_lse2 = s_delta + 2 * BT;                                // [2][128] written by compute warps
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_lse2 + 2 * BT);
+  uint8_t* sQ = smem + 2 * TILE_BYTES;                 // [Q_STAGES]
+  uint8_t* sdO = sQ + Q_STAGES * TILE_BYTES;           // [DO_STAGES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdO + DO_STAGES * TILE_BYTES);
   uint64_t* kv_full = bars;         // 1
-  uint64_t* qdo_full = bars + 1;    // [2]
-  uint64_t* qdo_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;      // 1
-  uint64_t* dp_full = bars + 6;     // 1
-  uint64_t* p_ready = bars + 7;     // 1 (128 arrivals)
-  uint64_t* ds_ready = bars + 8;    // 1 (128 arrivals)
-  uint64_t* acc_done = bars + 9;    // 1
-  uint64_t* drain_bar = bars + 10;  // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* q_full = bars + 1;      // [3]
+  uint64_t* q_empty = bars + 4;     // [3]
+  uint64_t* do_full = bars + 7;     // [2]
+  uint64_t* do_empty = bars + 9;    // [2]
+  uint64_t* s_full = bars + 11;     // 1
+  uint64_t* dp_full = bars + 12;    // 1
+  uint64_t* p_ready = bars + 13;    // 1 (one arrival per compute warp)
+  uint64_t* ds_ready = bars + 14;   // 1 (one arrival per compute warp)
+  uint64_t* acc_done = bars + 15;   // 1
+  uint64_t* drain_bar = bars + 16;  // 1
+  uint64_t* stat_ready = bars + 17; // [2] (one arrival per publishing warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stats = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + DKDV_BAR_BYTES);  // [2][256]
+  if (smem - smem_raw > DKDV_ALIGN_SLACK) {  // same verdict in every thread
+    if (threadIdx.x == 0) report(p.status, ZX_ERR_ARG, /*site=*/20, (int)(smem - smem_raw));
+    return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -171,20 +193,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&qdo_full[s], 1);
-      mbar_init(&qdo_empty[s], 1);
+    for (int s = 0; s < Q_STAGES; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    for (int s = 0; s < DO_STAGES; ++s) {
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 1);
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_ready, N_COMPUTE);
-    mbar_init(ds_ready, N_COMPUTE);
+    mbar_init(p_ready, KW_COMPUTE);      // per-warp arrivals
+    mbar_init(ds_ready, KW_COMPUTE);
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
+    mbar_init(&stat_ready[0], 8);
+    mbar_init(&stat_ready[1], 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == W_MMA) {
+  if (warp == KW_MMA) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -199,10 +227,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (tile_allowed(p, q_tile_pos(p, t), kpos0)) ++n_items;
   n_items *= G;
 
-  if (warp == W_PULL) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
+  if (warp == KW_PULL) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
 
-  if (n_items > 0 && warp < W_PULL) {
-    if (warp == W_TMA) {
+  if (n_items > 0 && warp < KW_PULL) {
+    if (warp == KW_TMA) {
       // ------------------------------- TMA producer -------------------------------
       if (lane == 0) {
         tma_prefetch_desc(&tmQ);
@@ -218,16 +246,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const int hq = hk * G + g;
           for (int t = 0; t < p.n_q_tiles; ++t) {
             if (!tile_allowed(p, q_tile_pos(p, t), kpos0)) continue;
-            const int s = n & 1;
-            if (!mbar_wait(&qdo_empty[s], ((n >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(&qdo_full[s], 2 * TILE_BYTES + 2 * BT * 4);
-            tma_load_4d(sQ + s * TILE_BYTES, &tmQ, &qdo_full[s], 0, hq, t * BT, b);
-            tma_load_4d(sQ + s * TILE_BYTES + HALF_BYTES, &tmQ, &qdo_full[s], 64, hq, t * BT, b);
-            tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &qdo_full[s], 0, hq, t * BT, b);
-            tma_load_4d(sdO + s * TILE_BYTES + HALF_BYTES, &tmdO, &qdo_full[s], 64, hq, t * BT, b);
-            const size_t row0 = ((size_t)b * p.Hq + hq) * p.Sq + (size_t)t * BT;
-            bulk_load_1d(s_lse + s * BT, p.lse + row0, BT * 4, &qdo_full[s]);
-            bulk_load_1d(s_delta + s * BT, p.delta + row0, BT * 4, &qdo_full[s]);
+            const int qs = n % Q_STAGES, ds = n % DO_STAGES;
+            if (!mbar_wait(&q_empty[qs], ((n / Q_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(&q_full[qs], TILE_BYTES);
+            tma_load_4d(sQ + qs * TILE_BYTES, &tmQ, &q_full[qs], 0, hq, t * BT, b);
+            tma_load_4d(sQ + qs * TILE_BYTES + HALF_BYTES, &tmQ, &q_full[qs], 64, hq, t * BT, b);
+            if (!mbar_wait(&do_empty[ds], ((n / DO_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(&do_full[ds], TILE_BYTES);
+            tma_load_4d(sdO + ds * TILE_BYTES, &tmdO, &do_full[ds], 0, hq, t * BT, b);
+            tma_load_4d(sdO + ds * TILE_BYTES + HALF_BYTES, &tmdO, &do_full[ds], 64, hq, t * BT, b);
             ++n;
           }
         }
@@ -238,7 +265,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
       }
-    } else if (warp == W_MMA) {
+    } else if (warp == KW_MMA) {
       // ------------------------------- MMA issuer ---------------------------------
       {  // all 32 lanes run this loop; the instructions themselves are issued by one elected lane
         constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);  // both operands K-major
@@ -248,7 +275,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint64_t q_k0 = base_kmajor(smem_u32(sQ)), do_k0 = base_kmajor(smem_u32(sdO));
         const uint64_t q_mn0 = base_mnmajor(smem_u32(sQ)), do_mn0 = base_mnmajor(smem_u32(sdO));
         bool ok = mbar_wait_w(kv_full, 0, abort_flag);
-        ok = ok && mbar_wait_w(&qdo_full[0], 0, abort_flag);
+        ok = ok && mbar_wait_w(&q_full[0], 0, abort_flag);
+        ok = ok && mbar_wait_w(&do_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
 #pragma unroll
@@ -260,31 +288,46 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         int n = 0;
         for (; n < n_items && ok; ++n) {
-          const int s = n & 1, sn = (n + 1) & 1;
+          const int qs = n % Q_STAGES, ds = n % DO_STAGES;
+          const int qsn = (n + 1) % Q_STAGES, dsn = (n + 1) % DO_STAGES;
           const bool has_next = n + 1 < n_items;
-          const uint64_t q_addr = desc_advance(q_mn0, (uint32_t)s * TILE_BYTES);     // read transposed
-          const uint64_t do_addr = desc_advance(do_mn0, (uint32_t)s * TILE_BYTES);   // read transposed
-          const uint64_t qn_addr = desc_advance(q_k0, (uint32_t)sn * TILE_BYTES);
-          const uint64_t don_addr = desc_advance(do_k0, (uint32_t)sn * TILE_BYTES);
+          const uint64_t q_addr = desc_advance(q_mn0, (uint32_t)qs * TILE_BYTES);     // read transposed
+          const uint64_t do_addr = desc_advance(do_mn0, (uint32_t)ds * TILE_BYTES);   // read transposed
+          const uint64_t qn_addr = desc_advance(q_k0, (uint32_t)qsn * TILE_BYTES);
+          const uint64_t don_addr = desc_advance(do_k0, (uint32_t)dsn * TILE_BYTES);
           // dV += P^T dO
           if (!mbar_wait_w(p_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
+          if (lane == 0) ZX_TRACE_DKDV(n, 8);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts_w(t_dv, t_s + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
+          for (int k = 0; k < 8; ++k) umma_ts_w(t_dv, t_s + (k >> 1) * 32 + (k & 1) * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_commit_w(&do_empty[ds]);   // dO(n) has now served dP^T(n) and dV(n)
+          if (lane == 0) ZX_TRACE_DKDV(n, 9);
           if (has_next) {
-            if (!mbar_wait_w(&qdo_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_w(&q_full[qsn], ((n + 1) / Q_STAGES) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
+            if (lane == 0) ZX_TRACE_DKDV(n, 10);
 #pragma unroll
             for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(k_addr, k), desc_kmajor(qn_addr, k), idesc_kk, k > 0);
             umma_commit_w(s_full);
+            if (lane == 0) ZX_TRACE_DKDV(n, 15);
+            if (p.trace != nullptr && blockIdx.x == 0) {
+              mbar_wait_w(s_full, (n + 1) & 1, abort_flag);
+              if (lane == 0) ZX_TRACE_DKDV(n, 14);
+            }
           }
           // dK += dS^T Q
           if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
+          if (lane == 0) ZX_TRACE_DKDV(n, 11);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts_w(t_dk, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
-          umma_commit_w(&qdo_empty[s]);
+          for (int k = 0; k < 8; ++k) umma_ts_w(t_dk, t_dp + (k >> 1) * 32 + (k & 1) * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_commit_w(&q_empty[qs]);    // Q(n) has now served S^T(n) and dK(n)
+          if (lane == 0) ZX_TRACE_DKDV(n, 12);
           if (has_next) {
+            if (!mbar_wait_w(&do_full[dsn], ((n + 1) / DO_STAGES) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            if (lane == 0) ZX_TRACE_DKDV(n, 13);
 #pragma unroll
             for (int k = 0; k < 8; ++k)
               umma_ss_w(t_dp, desc_kmajor(v_addr, k), desc_kmajor(don_addr, k), idesc_kk, k > 0);
@@ -302,38 +345,70 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     } else {
       // ------------------------------- compute warps ------------------------------
-      // Two warpgroups: warpgroup wg owns query columns [64 wg, 64 wg + 64) of every KV row.
+      // Four column groups: group wg owns query columns [32 wg, 32 wg + 32) of every KV row.
       const int wg = warp >> 2;
       const int lq = warp & 3;                 // TMEM lane quarter
       const int r = lq * 32 + lane;            // KV row of this thread == TMEM lane
-      const int col0 = wg * 64;
+      const int col0 = wg * 32;
       const uint32_t lane_base = (uint32_t)(lq * 32) << 16;
       const uint32_t t_s = tmem_base + lane_base + col0, t_dp = tmem_base + lane_base + 128 + col0;
       const int my_kpos = kpos0 + r;
       uint32_t n = 0;
       bool ok = true;
-      for (int g = 0; g < G && ok; ++g) {
-        for (int t = 0; t < p.n_q_tiles; ++t) {
-          const int qpos0 = q_tile_pos(p, t);
-          if (!tile_allowed(p, qpos0, kpos0)) continue;
-          const int s = n & 1;
-          if (!wait_warp(&qdo_full[s], (n >> 1) & 1, abort_flag)) { ok = false; break; }
-          if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          uint32_t sr[64];
-          tmem_ld_32x32b_x32(t_s + 0, sr);
-          tmem_ld_32x32b_x32(t_s + 32, sr + 32);
-          tmem_wait_ld();
-          const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
-          // packed fp32x2 math: two query columns per instruction
-          const float2* lse_nat2 = reinterpret_cast<const float2*>(s_lse + s * BT + col0);
-          const int qp = qpos0 + col0;   // column c is query qp + c; it sees this key iff my_kpos <= qp + c
-          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
-          const float2 nlog2e = make_float2(-LOG2E, -LOG2E);
+      // Per-query statistics reach the math through shared memory, one item ahead: thread i of
+      // the 256 fetches one value of the NEXT item (-lse * log2e for i < 128, -delta otherwise)
+      // at the top of an iteration and publishes it at the bottom, so no global-load latency
+      // sits between a TMEM read and its use. Buffer (n + 1) & 1 was last read in iteration
+      // n - 1, and every thread finished that before dP^T(n) could be issued.
+      const int ct = threadIdx.x;  // 0..255
+      auto stat_fetch = [&](int g, int t) -> float {
+        const size_t base = ((size_t)b * p.Hq + (hk * G + g)) * p.Sq + (size_t)t * BT;
+        return ct < BT ? -LOG2E * __ldg(p.lse + base + ct) : -__ldg(p.delta + base + (ct - BT));
+      };
+      auto next_item = [&](int& g, int& t) -> bool {
+        for (;;) {
+          if (++t >= p.n_q_tiles) {
+            t = 0;
+            if (++g >= G) return false;
+          }
+          if (tile_allowed(p, q_tile_pos(p, t), kpos0)) return true;
+        }
+      };
+      int g = 0, t = -1;
+      bool have = next_item(g, t);
+      if (have && ct < 256) {
+        stats[ct] = stat_fetch(g, t);
+        mbar_arrive_warp(&stat_ready[0]);
+      }
+      while (have) {
+        int gn = g, tn = t;
+        const bool have_next = next_item(gn, tn);
+        float pre = 0.f;
+        if (have_next && ct < 256) pre = stat_fetch(gn, tn);
+        const int qpos0 = q_tile_pos(p, t);
+        const float* st = stats + (n & 1) * 256;
+        if (!wait_warp(&stat_ready[n & 1], (n >> 1) & 1, abort_flag)) { ok = false; break; }
+        ZX_TRACE_W(n, 7);
+        if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (threadIdx.x == 0) ZX_TRACE_DKDV(n, 0);
+        ZX_TRACE_W(n, 0);
+        uint32_t sr[32];
+        tmem_ld_32x32b_x32(t_s, sr);
+        tmem_wait_ld();
+        ZX_TRACE_W(n, 1);
+        const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
+        const int qp = qpos0 + col0;   // column c is query qp + c; it sees this key iff my_kpos <= qp + c
+        const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
+        const float4* nl4 = reinterpret_cast<const float4*>(st + col0);   // uniform address: broadcast reads
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 nl = nl4[c4];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = 2 * c4 + h;
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2,
-                                        __fmul2_rn(lse_nat2[c], nlog2e));
+                                        h == 0 ? make_float2(nl.x, nl.y) : make_float2(nl.z, nl.w));
             float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
             if (diag) {
               if (my_kpos > qp + 2 * c) p0 = 0.f;
@@ -342,69 +417,84 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             sr[2 * c] = __float_as_uint(p0);
             sr[2 * c + 1] = __float_as_uint(p1);
           }
-          {
-            // bf16 P^T for this half goes over the first 32 columns of the half this thread just read
-            uint32_t pk[32];
+        }
+        ZX_TRACE_W(n, 2);
+        {
+          // bf16 P^T of this group goes over the first 16 of the 32 columns this thread just read
+          uint32_t pk[16];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) pk[c] = pack_bf16x2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
-            tmem_st_32x32b_x32(t_s, pk);
-          }
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(p_ready);
-          if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const float2* dl2 = reinterpret_cast<const float2*>(s_delta + s * BT + col0);
-          uint32_t dp[64];
-          tmem_ld_32x32b_x32(t_dp + 0, dp);
-          tmem_ld_32x32b_x32(t_dp + 32, dp + 32);
-          tmem_wait_ld();
-          {
-            uint32_t dsp[32];
+          for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
+          tmem_st_32x32b_x16(t_s, pk);
+        }
+        tmem_wait_st();
+        if (threadIdx.x == 0) ZX_TRACE_DKDV(n, 2);
+        ZX_TRACE_W(n, 3);
+        tc_fence_before();
+        mbar_arrive_warp(p_ready);
+        if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (threadIdx.x == 0) ZX_TRACE_DKDV(n, 3);
+        ZX_TRACE_W(n, 4);
+        uint32_t dp[32];
+        tmem_ld_32x32b_x32(t_dp, dp);
+        tmem_wait_ld();
+        ZX_TRACE_W(n, 5);
+        {
+          uint32_t dsp[16];
+          const float4* nd4 = reinterpret_cast<const float4*>(st + BT + col0);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float2 dl = dl2[e];
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 nd = nd4[e4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int e = 2 * e4 + h;
               const float2 t2 = __fadd2_rn(make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])),
-                                           make_float2(-dl.x, -dl.y));
+                                           h == 0 ? make_float2(nd.x, nd.y) : make_float2(nd.z, nd.w));
               const float2 d = __fmul2_rn(make_float2(__uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1])), t2);
               dsp[e] = pack_bf16x2(d.x, d.y);
             }
-            tmem_st_32x32b_x32(t_dp, dsp);
           }
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(ds_ready);
-          ++n;
+          tmem_st_32x32b_x16(t_dp, dsp);
         }
+        tmem_wait_st();
+        if (threadIdx.x == 0) ZX_TRACE_DKDV(n, 5);
+        ZX_TRACE_W(n, 6);
+        tc_fence_before();
+        mbar_arrive_warp(ds_ready);
+        if (have_next && ct < 256) {
+          stats[((n + 1) & 1) * 256 + ct] = pre;
+          mbar_arrive_warp(&stat_ready[(n + 1) & 1]);
+        }
+        g = gn;
+        t = tn;
+        have = have_next;
+        ++n;
       }
       // epilogue: add dV and scale * dK into the (possibly remote) fp32 accumulators; each
-      // warpgroup drains its 64 columns of both accumulators
+      // column group drains its 32 columns of both accumulators
       if (ok) ok = wait_warp(acc_done, 0, abort_flag);
       tc_fence_after();
       if (ok) {
         const size_t row_off = (((size_t)b * p.Skv + (size_t)j * BT + r) * p.Hkv + hk) * HD + col0;
         float* dv_row = p.dv + row_off;
         float* dk_row = p.dk + row_off;
-#pragma unroll
-        for (int ci = 0; ci < 2; ++ci) {
+        {
           uint32_t a[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_base + 256 + col0 + ci * 32, a);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + 256 + col0, a);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 8; ++e)
-            red_add_v4_sys(dv_row + ci * 32 + e * 4, __uint_as_float(a[4 * e]), __uint_as_float(a[4 * e + 1]),
+            red_add_v4_sys(dv_row + e * 4, __uint_as_float(a[4 * e]), __uint_as_float(a[4 * e + 1]),
                            __uint_as_float(a[4 * e + 2]), __uint_as_float(a[4 * e + 3]));
         }
-#pragma unroll
-        for (int ci = 0; ci < 2; ++ci) {
+        {
           uint32_t a[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_base + 384 + col0 + ci * 32, a);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + 384 + col0, a);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 8; ++e)
-            red_add_v4_sys(dk_row + ci * 32 + e * 4, __uint_as_float(a[4 * e]) * p.scale,
-                           __uint_as_float(a[4 * e + 1]) * p.scale, __uint_as_float(a[4 * e + 2]) * p.scale,
-                           __uint_as_float(a[4 * e + 3]) * p.scale);
+            red_add_v4_sys(dk_row + e * 4, __uint_as_float(a[4 * e]) * p.scale, __uint_as_float(a[4 * e + 1]) * p.scale,
+                           __uint_as_float(a[4 * e + 2]) * p.scale, __uint_as_float(a[4 * e + 3]) * p.scale);
         }
       }
       if (!ok && lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/23, (int)n);
@@ -413,7 +503,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   tc_fence_before();
   __syncthreads();
-  if (warp == W_MMA) {
+  if (warp == KW_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -422,7 +512,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // ------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------
-constexpr int DQ_SMEM = 2 * TILE_BYTES /*Q,dO*/ + 4 * TILE_BYTES /*K,V x2*/ + 1024 + 256;
+// K lives until dQ of its item has been issued, V only until dP: a 3-deep K ring and a 2-deep V
+// ring free every slot a full iteration before its next tile is needed (hides the TMA latency).
+constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int DQ_SMEM = 2 * TILE_BYTES /*Q,dO*/ + (K_STAGES + V_STAGES) * TILE_BYTES + 1024 + 256;
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
@@ -431,19 +524,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + TILE_BYTES;
-  uint8_t* sK = smem + 2 * TILE_BYTES;  // [2]
-  uint8_t* sV = smem + 4 * TILE_BYTES;  // [2]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint8_t* sK = smem + 2 * TILE_BYTES;            // [K_STAGES]
+  uint8_t* sV = sK + K_STAGES * TILE_BYTES;       // [V_STAGES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + V_STAGES * TILE_BYTES);
   uint64_t* qdo_full = bars;       // 1
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;     // 1
-  uint64_t* dp_full = bars + 6;    // 1
-  uint64_t* s_read = bars + 7;     // 1 (128 arrivals)
-  uint64_t* ds_ready = bars + 8;   // 1 (128 arrivals)
-  uint64_t* acc_done = bars + 9;   // 1
-  uint64_t* drain_bar = bars + 10; // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 1;     // [3]
+  uint64_t* k_empty = bars + 4;    // [3]
+  uint64_t* v_full = bars + 7;     // [2]
+  uint64_t* v_empty = bars + 9;    // [2]
+  uint64_t* s_full = bars + 11;    // 1
+  uint64_t* dp_full = bars + 12;   // 1
+  uint64_t* s_read = bars + 13;    // 1 (one arrival per compute warp)
+  uint64_t* ds_ready = bars + 14;  // 1 (one arrival per compute warp)
+  uint64_t* acc_done = bars + 15;  // 1
+  uint64_t* drain_bar = bars + 16; // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -458,14 +553,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(s_read, N_COMPUTE);
-    mbar_init(ds_ready, N_COMPUTE);
+    mbar_init(s_read, N_COMPUTE / 32);    // per-warp arrivals
+    mbar_init(ds_ready, N_COMPUTE / 32);
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -498,13 +597,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         bool ok = true;
         for (int j = 0; j < p.n_kv_tiles; ++j) {
           if (!tile_allowed(p, qpos0, kv_tile_pos(p, j))) continue;
-          const int s = n & 1;
-          if (!mbar_wait(&kv_empty[s], ((n >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-          tma_load_4d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, hk, j * BT, b);
-          tma_load_4d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &kv_full[s], 64, hk, j * BT, b);
-          tma_load_4d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, hk, j * BT, b);
-          tma_load_4d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &kv_full[s], 64, hk, j * BT, b);
+          const int ks = n % K_STAGES, vs = n % V_STAGES;
+          if (!mbar_wait(&k_empty[ks], ((n / K_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&k_full[ks], TILE_BYTES);
+          tma_load_4d(sK + ks * TILE_BYTES, &tmK, &k_full[ks], 0, hk, j * BT, b);
+          tma_load_4d(sK + ks * TILE_BYTES + HALF_BYTES, &tmK, &k_full[ks], 64, hk, j * BT, b);
+          if (!mbar_wait(&v_empty[vs], ((n / V_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&v_full[vs], TILE_BYTES);
+          tma_load_4d(sV + vs * TILE_BYTES, &tmV, &v_full[vs], 0, hk, j * BT, b);
+          tma_load_4d(sV + vs * TILE_BYTES + HALF_BYTES, &tmV, &v_full[vs], 64, hk, j * BT, b);
           ++n;
         }
         if (!ok) {
@@ -523,7 +624,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint64_t k_k0 = base_kmajor(smem_u32(sK)), v_k0 = base_kmajor(smem_u32(sV));
         const uint64_t k_mn0 = base_mnmajor(smem_u32(sK));
         bool ok = mbar_wait_w(qdo_full, 0, abort_flag);
-        ok = ok && mbar_wait_w(&kv_full[0], 0, abort_flag);
+        ok = ok && mbar_wait_w(&k_full[0], 0, abort_flag);
+        ok = ok && mbar_wait_w(&v_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
 #pragma unroll
@@ -532,17 +634,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(v_k0, k), idesc_kk, k > 0);
           umma_commit_w(dp_full);
+          umma_commit_w(&v_empty[0]);
         }
         int n = 0;
         for (; n < n_items && ok; ++n) {
-          const int s = n & 1, sn = (n + 1) & 1;
+          const int ks = n % K_STAGES, ksn = (n + 1) % K_STAGES, vsn = (n + 1) % V_STAGES;
           const bool has_next = n + 1 < n_items;
-          const uint64_t k_addr = desc_advance(k_mn0, (uint32_t)s * TILE_BYTES);   // read transposed
-          const uint64_t kn_addr = desc_advance(k_k0, (uint32_t)sn * TILE_BYTES);
-          const uint64_t vn_addr = desc_advance(v_k0, (uint32_t)sn * TILE_BYTES);
+          const uint64_t k_addr = desc_advance(k_mn0, (uint32_t)ks * TILE_BYTES);   // read transposed
+          const uint64_t kn_addr = desc_advance(k_k0, (uint32_t)ksn * TILE_BYTES);
+          const uint64_t vn_addr = desc_advance(v_k0, (uint32_t)vsn * TILE_BYTES);
           if (has_next) {
             if (!mbar_wait_w(s_read, n & 1, abort_flag)) { ok = false; break; }
-            if (!mbar_wait_w(&kv_full[sn], ((n + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_w(&k_full[ksn], ((n + 1) / K_STAGES) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(q_addr, k), desc_kmajor(kn_addr, k), idesc_kk, k > 0);
@@ -553,13 +656,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (lane == 0) ZX_TRACE(n, 8);
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_ts_w(t_dq, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
-          umma_commit_w(&kv_empty[s]);
+          umma_commit_w(&k_empty[ks]);    // K(n) has now served S(n) and dQ(n)
           if (lane == 0) ZX_TRACE(n, 9);
           if (has_next) {
+            if (!mbar_wait_w(&v_full[vsn], ((n + 1) / V_STAGES) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 8; ++k)
               umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(vn_addr, k), idesc_kk, k > 0);
             umma_commit_w(dp_full);
+            umma_commit_w(&v_empty[vsn]);   // V(n+1) is only read by dP(n+1)
           }
           if (lane == 0) ZX_TRACE(n, 10);
         }
@@ -599,7 +705,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_wait_ld();
         if (threadIdx.x == 0) ZX_TRACE(n, 1);
         tc_fence_before();
-        mbar_arrive(s_read);
+        mbar_arrive_warp(s_read);
         const bool diag = p.causal && (kpos0 + BT - 1 > qpos0);
         const int kp = kpos0 + col0;
         const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
@@ -627,7 +733,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (threadIdx.x == 0) ZX_TRACE(n, 4);
         {
           uint32_t dsp[32];
-#pragma unroll
           const float2 ndl = make_float2(-dlt, -dlt);
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
@@ -642,7 +747,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (threadIdx.x == 0) ZX_TRACE(n, 5);
         if (threadIdx.x == 160) ZX_TRACE(n, 13);
         tc_fence_before();
-        mbar_arrive(ds_ready);
+        mbar_arrive_warp(ds_ready);
         ++n;
       }
       if (ok) ok = wait_warp(acc_done, 0, abort_flag);

@@ -120,7 +120,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 4);   // one arrival per softmax warp
       mbar_init(&o_done[i], 1);
     }
     mbar_init(drain_bar, 1);
@@ -340,7 +340,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_st_32x32b_x32(s_tmem + 32, pk + 32);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_ready[i]);
+        mbar_arrive_warp(&p_ready[i]);
         ++cnt;
       }
 

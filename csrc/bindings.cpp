@@ -189,7 +189,7 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.pull_dst = reinterpret_cast<void*>(pull_dst);
   a.pull_bytes = (size_t)pull_bytes;
   if (trace.has_value()) {
-    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 64 * 16, "trace: int64[1024]");
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 3072, "trace: int64[3072]");
     a.trace = reinterpret_cast<long long*>(trace->data_ptr());
   }
   a.status = status_ptr();

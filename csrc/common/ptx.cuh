@@ -58,6 +58,14 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival per warp: an arrive is an atomic on one shared-memory word, so 32 lanes arriving
+// separately serialise (a 512-thread arrival costs over a thousand cycles of the item's critical
+// path). The warp converges first, which also orders every lane's earlier writes before the
+// single arrive. Barriers used with this are initialised with their WARP count.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -82,13 +90,48 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #define ZX_WAIT_LIMIT_NS 2000000000ull
 #endif
 
+#ifndef ZX_WAIT_MODE
+#define ZX_WAIT_MODE 0
+#define ZX_WAIT_HINT 0
+#endif
 // Bounded wait. Returns false when the wait gave up (its own limit, or another role already
 // raised *abort). The caller must then fall through to the kernel's teardown.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
+#if ZX_WAIT_MODE == 0
   for (int i = 0; i < 1024; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
+#elif ZX_WAIT_MODE == 1
+  for (int i = 0; i < 100000; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)ZX_WAIT_HINT)
+        : "memory");
+    if (ok) return true;
+  }
+#else
+  for (int i = 0; i < 100000; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    __nanosleep(ZX_WAIT_HINT);
+  }
+#endif
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {

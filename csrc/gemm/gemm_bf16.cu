@@ -78,7 +78,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 128);
+      mbar_init(&acc_empty[b], 4);   // one arrival per epilogue warp
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -254,7 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(&acc_empty[buf]);
+      mbar_arrive_warp(&acc_empty[buf]);
     }
     if (!ok && lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/3, (int)lt);
   }
