@@ -62,7 +62,9 @@ std::vector<int64_t> read_status(bool clear) {
 
 // out[M,N] = a @ b^T (+ addend) with optional transposed storage of either operand.
 //   a: [M,K] (a_t=false) or [K,M] (a_t=true); b: [N,K] (b_t=false) or [K,N] (b_t=true)
-void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_t, bool b_t, const c10::optional<Tensor>& addend) {
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_t, bool b_t, const c10::optional<Tensor>& addend,
+          int64_t pull_src, int64_t pull_dst, int64_t pull_bytes, const std::vector<int64_t>& scatter_ptrs,
+          int64_t scatter_rows_per_rank, int64_t scatter_src_rank) {
   check_bf16(a, "a");
   check_bf16(b, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm expects matrices");
@@ -76,7 +78,12 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_t, bool b_t, con
   g.N = (int)(b_t ? b.size(1) : b.size(0));
   const int64_t kb = b_t ? b.size(0) : b.size(1);
   TORCH_CHECK(kb == g.K, "gemm: inner dimensions differ (", g.K, " vs ", kb, ")");
-  TORCH_CHECK(out.size(0) == g.M && out.size(1) == g.N, "gemm: out has the wrong shape");
+  if (scatter_ptrs.empty()) {
+    TORCH_CHECK(out.size(0) == g.M && out.size(1) == g.N, "gemm: out has the wrong shape");
+  } else {  // `out` is one receive slot of this rank: one rank's rows of the result, bf16
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.size(0) == scatter_rows_per_rank && out.size(1) == g.N,
+                "gemm: a scattered result needs a bf16 [rows_per_rank, N] slot");
+  }
   g.A = a.data_ptr();
   g.B = b.data_ptr();
   g.C = out.data_ptr();
@@ -94,6 +101,17 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_t, bool b_t, con
     g.D = d.data_ptr();
     g.ldd = (int)d.stride(0);
     g.d_mode = d.scalar_type() == torch::kFloat32 ? 2 : 1;
+  }
+  g.pull_src = reinterpret_cast<const void*>(pull_src);
+  g.pull_dst = reinterpret_cast<void*>(pull_dst);
+  g.pull_bytes = (size_t)pull_bytes;
+  if (!scatter_ptrs.empty()) {
+    TORCH_CHECK(scatter_ptrs.size() <= 8 && scatter_rows_per_rank > 0, "gemm: at most 8 scatter targets");
+    TORCH_CHECK(!addend.has_value(), "gemm: a scattered result takes no addend");
+    g.scatter_ranks = (int)scatter_ptrs.size();
+    g.scatter_rows_per_rank = (int)scatter_rows_per_rank;
+    g.scatter_src_rank = (int)scatter_src_rank;
+    for (size_t r = 0; r < scatter_ptrs.size(); ++r) g.scatter_base[r] = reinterpret_cast<void*>(scatter_ptrs[r]);
   }
   g.status = status_ptr();
   g.stream = cur_stream();
@@ -386,6 +404,15 @@ void sumsq(const Tensor& g, Tensor& out) {
   zx::launch_sumsq(g.data_ptr<float>(), (size_t)g.numel(), out.data_ptr<float>(), sm_count(), cur_stream());
   check_launch("sumsq");
 }
+void sum_slots_bf16(const Tensor& slots, int64_t ranks, Tensor& out) {
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == torch::kBFloat16 && slots.is_contiguous(), "sum_slots: slots");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.numel() % 8 == 0 &&
+                  slots.numel() == ranks * out.numel(),
+              "sum_slots: out must be contiguous bf16 with numel a multiple of 8 and slots = ranks x out");
+  c10::cuda::CUDAGuard guard(out.device());
+  zx::launch_sum_slots_bf16(slots.data_ptr(), (int)ranks, (size_t)out.numel(), out.data_ptr(), sm_count(), cur_stream());
+  check_launch("sum_slots_bf16");
+}
 void clip_coef(const Tensor& ss, double scale, double max_norm, Tensor& coef, Tensor& norm_out) {
   c10::cuda::CUDAGuard guard(ss.device());
   zx::launch_clip_coef(ss.data_ptr<float>(), (float)scale, (float)max_norm, coef.data_ptr<float>(),
@@ -474,7 +501,9 @@ void zero_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("read_status", &read_status, "read (and optionally clear) the kernel status word");
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_t"), py::arg("b_t"), py::arg("addend"),
+        py::arg("pull_src") = 0, py::arg("pull_dst") = 0, py::arg("pull_bytes") = 0,
+        py::arg("scatter_ptrs") = std::vector<int64_t>{}, py::arg("scatter_rows_per_rank") = 0, py::arg("scatter_src_rank") = 0);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("d_o"), py::arg("lse"),
         py::arg("delta"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("scale"), py::arg("causal"),
@@ -495,6 +524,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw", &adamw);
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);
+  m.def("sum_slots_bf16", &sum_slots_bf16);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_export", &peer_export);
   m.def("peer_open", &peer_open);

@@ -475,6 +475,33 @@ __global__ void adamw_kernel(uint16_t* __restrict__ p_hi, int16_t* __restrict__ 
   }
 }
 
+// out[i] = sum over r of slots[r * n + i]: second half of the fused reduce-scatter (the GEMM epilogues of
+// every rank stored their bf16 partial rows into this rank's slots); fp32 sum, one rounding.
+__global__ void sum_slots_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int ranks, size_t n,
+                                      __nv_bfloat16* __restrict__ out) {
+  const size_t nvec = n >> 3;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < ranks; ++r) {
+      const uint4 v = reinterpret_cast<const uint4*>(slots + (size_t)r * n)[i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      ow[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 // sum of squares of a flat fp32 buffer, accumulated into out[0] (caller zeroes it)
 __global__ void sumsq_kernel(const float* __restrict__ g, size_t n, float* __restrict__ out) {
   __shared__ float s[32];
@@ -595,6 +622,11 @@ void launch_adamw(void* p_hi, void* p_lo, float* m, float* v, const float* g, si
   adamw_kernel<<<grid_for(n / 4, 256, sm_count), 256, 0, st>>>((uint16_t*)p_hi, (int16_t*)p_lo, m, v, g, n, lr, beta1,
                                                                beta2, eps, weight_decay, bias1, bias2, grad_scale,
                                                                grad_scale_ptr);
+}
+void launch_sum_slots_bf16(const void* slots, int ranks, size_t n, void* out, int sm_count, cudaStream_t st) {
+  if (n == 0) return;
+  sum_slots_bf16_kernel<<<grid_for(n / 8, 256, sm_count), 256, 0, st>>>((const __nv_bfloat16*)slots, ranks, n,
+                                                                         (__nv_bfloat16*)out);
 }
 void launch_sumsq(const float* g, size_t n, float* out, int sm_count, cudaStream_t st) {
   if (n == 0) return;

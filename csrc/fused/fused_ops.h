@@ -30,6 +30,8 @@ void launch_kv_dequant_e4m3(const void* q, const float* scales, void* x, size_t 
 void launch_adamw(void* p_hi, void* p_lo, float* m, float* v, const float* g, size_t n, float lr, float beta1,
                   float beta2, float eps, float weight_decay, int step, float grad_scale, const float* grad_scale_ptr,
                   int sm_count, cudaStream_t st);
+// out[i] = sum_r slots[r * n + i] (bf16 in, fp32 sum, bf16 out); n a multiple of 8
+void launch_sum_slots_bf16(const void* slots, int ranks, size_t n, void* out, int sm_count, cudaStream_t st);
 void launch_sumsq(const float* g, size_t n, float* out, int sm_count, cudaStream_t st);
 void launch_clip_coef(const float* sumsq, float scale, float max_norm, float* coef, float* norm_out, cudaStream_t st);
 

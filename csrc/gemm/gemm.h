@@ -19,6 +19,21 @@ struct GemmArgs {
   bool a_mn = false, b_mn = false;
   int out_fp32 = 0;  // C is fp32 instead of bf16
   int d_mode = 0;    // 0: no addend, 1: bf16 addend, 2: fp32 addend
+  // Fused all-gather: while the tiles compute, one extra warp per CTA copies this CTA's slice of a
+  // (possibly peer-resident) buffer into local memory with plain 16-byte loads, so the operand of
+  // the NEXT launch crosses NVLink underneath this launch's math. Sizes in bytes, multiples of 16.
+  const void* pull_src = nullptr;
+  void* pull_dst = nullptr;
+  size_t pull_bytes = 0;
+  // Fused reduce-scatter, first half: instead of one C, every row block is STORED (bf16) into the
+  // receive slot that its owner keeps for this rank: row m goes to
+  //   scatter_base[m / rows_per_rank] + (scatter_src_rank * rows_per_rank + m % rows_per_rank) * ldc.
+  // The bases are peer-mapped pointers, so the partial tiles cross NVLink as the accumulators drain;
+  // after a barrier the owner sums its `scatter_ranks` slots (sum_slots_bf16).
+  int scatter_ranks = 0;
+  int scatter_rows_per_rank = 0;
+  int scatter_src_rank = 0;
+  void* scatter_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   Status* status = nullptr;
   cudaStream_t stream = nullptr;
   int sm_count = 148;

@@ -24,7 +24,8 @@ constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int CHUNK_BYTES = 64 * BK * 2;    // one 64-wide MN chunk of an MN-major tile: 8 KB
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 224;   // TMA, MMA, four epilogue warps, one peer-pull warp
+constexpr int W_PULL = 6;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 
@@ -36,6 +37,11 @@ struct KParams {
   int out_fp32;
   int d_mode;  // 0: none, 1: bf16 addend, 2: fp32 addend
   int num_m, num_n;
+  const uint4* pull_src;
+  uint4* pull_dst;
+  size_t pull_nvec;
+  int scatter_ranks, scatter_rows_per_rank, scatter_src_rank;
+  __nv_bfloat16* scatter_base[8];
   Status* status;
 };
 
@@ -178,6 +184,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
+  } else if (warp == W_PULL) {
+    // ------------------------------- peer pull ----------------------------------
+    warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
   } else {
     // ------------------------------- epilogue warps -----------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -238,7 +247,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
             }
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0);
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc;
+            if (p.scatter_ranks > 0) {
+              // reduce-scatter fused into the epilogue: this partial row goes to the slot its owner keeps for us
+              const int owner = row / p.scatter_rows_per_rank;
+              crow = p.scatter_base[owner] +
+                     ((size_t)p.scatter_src_rank * p.scatter_rows_per_rank + (row - owner * p.scatter_rows_per_rank)) * p.ldc;
+            }
+            uint4* dst = reinterpret_cast<uint4*>(crow + col0);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               if (col0 + g * 8 < p.N) {
@@ -290,6 +306,16 @@ void launch_gemm_bf16(const GemmArgs& a) {
     throw std::runtime_error("gemm_bf16: leading dimensions must keep rows 16-byte aligned");
   if (a.d_mode != 0 && (a.D == nullptr || a.ldd % (a.d_mode == 2 ? 4 : 8) != 0))
     throw std::runtime_error("gemm_bf16: bad addend");
+  if (a.pull_bytes % 16 != 0 || (a.pull_bytes != 0 && (a.pull_src == nullptr || a.pull_dst == nullptr)))
+    throw std::runtime_error("gemm_bf16: the pulled range must be a multiple of 16 bytes with both ends given");
+  if (a.scatter_ranks != 0) {
+    if (a.scatter_ranks < 1 || a.scatter_ranks > 8 || a.scatter_rows_per_rank <= 0 ||
+        a.scatter_rows_per_rank * a.scatter_ranks < a.M || a.ldc % 8 != 0 || a.out_fp32 || a.scatter_src_rank < 0 ||
+        a.scatter_src_rank >= a.scatter_ranks)
+      throw std::runtime_error("gemm_bf16: bad scatter description");
+    for (int r = 0; r < a.scatter_ranks; ++r)
+      if (a.scatter_base[r] == nullptr) throw std::runtime_error("gemm_bf16: missing scatter base");
+  }
 
   // K-major operand: global [rows, K]; box 64 (K) x rows-per-tile.
   // MN-major operand: global [K, rows]; box 64 (rows) x 64 (K), several boxes per stage.
@@ -304,6 +330,13 @@ void launch_gemm_bf16(const GemmArgs& a) {
   p.out_fp32 = a.out_fp32; p.d_mode = a.d_mode;
   p.num_m = (a.M + BM - 1) / BM;
   p.num_n = (a.N + BN - 1) / BN;
+  p.pull_src = reinterpret_cast<const uint4*>(a.pull_src);
+  p.pull_dst = reinterpret_cast<uint4*>(a.pull_dst);
+  p.pull_nvec = a.pull_bytes / 16;
+  p.scatter_ranks = a.scatter_ranks;
+  p.scatter_rows_per_rank = a.scatter_rows_per_rank;
+  p.scatter_src_rank = a.scatter_src_rank;
+  for (int r = 0; r < 8; ++r) p.scatter_base[r] = reinterpret_cast<__nv_bfloat16*>(a.scatter_base[r]);
   p.status = a.status;
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < a.sm_count ? tiles : a.sm_count;

@@ -136,6 +136,34 @@ def case_train(ctx):
     print(f"rank {ctx.rank}: train ok", flush=True)
 
 
+def case_tp(ctx):
+    """all-gather fused into the GEMM (pull warp) and GEMM with a reduce-scatter epilogue (peer red.add),
+    against fp32 math on the gathered operands; two calls in a row reuse the buffers."""
+    from zenyx_b200.ops import _ext
+    from zenyx_b200.parallel.fused_collective import FusedCollectiveContext, allgather_gemm, gemm_reduce_scatter
+
+    R, r = ctx.world_size, ctx.rank
+    m, K, N = 384, 512, 768
+    fc = FusedCollectiveContext(m, K, N)
+    for trial in range(2):
+        gen = torch.Generator().manual_seed(100 + trial)
+        x_all = torch.randn(R * m, K, generator=gen)
+        w = (torch.randn(N, K, generator=gen) / math.sqrt(K))
+        y = allgather_gemm(x_all[r * m: (r + 1) * m].cuda().bfloat16(), w.cuda().bfloat16(), fc)
+        _ext.check_status()
+        ref = x_all.bfloat16().float() @ w.bfloat16().float().t()
+        assert rel(y.cpu(), ref) < 1e-2, ("allgather_gemm", trial, rel(y.cpu(), ref))
+        # row-parallel: each rank holds K/R input features of every row
+        Kl = K // R
+        xr = x_all[:, r * Kl: (r + 1) * Kl].cuda().bfloat16()
+        wr = w[:, r * Kl: (r + 1) * Kl].cuda().bfloat16()
+        yr = gemm_reduce_scatter(xr, wr, fc)
+        _ext.check_status()
+        assert rel(yr.cpu(), ref[r * m: (r + 1) * m]) < 1e-2, ("gemm_reduce_scatter", trial, rel(yr.cpu(), ref[r * m: (r + 1) * m]))
+    fc.close()
+    print(f"rank {r}: tp ok", flush=True)
+
+
 def main():
     from zenyx_b200.parallel.communication import init_distributed_from_env
 

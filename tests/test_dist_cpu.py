@@ -133,6 +133,47 @@ def test_tensor_parallel_layers_forward_and_backward():
 
 
 # ------------------------------------------------------------------------------------------------
+def _sequence_parallel_linears(rank, world):
+    """all-gather -> GEMM and GEMM -> reduce-scatter (host fallbacks of the fused kernels) and the
+    two sequence-parallel layers: forward and every gradient against a single-process MLP."""
+    from zenyx_b200.distributed import SequenceParallelColumnLinear, SequenceParallelRowLinear
+    from zenyx_b200.parallel.fused_collective import allgather_gemm, gemm_reduce_scatter
+
+    torch.manual_seed(5)
+    m, K, H, N = 6, 8, 12, 8
+    x_all = torch.randn(world * m, K)
+    w1, w2 = torch.randn(H, K) / 3, torch.randn(N, H) / 3
+    y = allgather_gemm(x_all[rank * m:(rank + 1) * m], w1)
+    assert torch.allclose(y, x_all @ w1.t(), atol=1e-5)
+    kl = K // world
+    yr = gemm_reduce_scatter(x_all[:, rank * kl:(rank + 1) * kl].contiguous(), w1[:, rank * kl:(rank + 1) * kl].contiguous())
+    assert torch.allclose(yr, (x_all @ w1.t())[rank * m:(rank + 1) * m], atol=1e-5)
+    # column (token-sharded input) -> tanh -> row (token-sharded output)
+    xr = x_all.clone().requires_grad_(True)
+    ref = torch.tanh(xr @ w1.t()) @ w2.t()
+    ref.square().sum().backward()
+    hl = H // world
+    col = SequenceParallelColumnLinear(K, H, dtype=torch.float32)
+    row = SequenceParallelRowLinear(H, N, dtype=torch.float32)
+    with torch.no_grad():
+        col.weight.copy_(w1[rank * hl:(rank + 1) * hl])
+        row.weight.copy_(w2[:, rank * hl:(rank + 1) * hl])
+    xl = x_all[rank * m:(rank + 1) * m].clone().requires_grad_(True)
+    out = row(torch.tanh(col(xl)))
+    assert torch.allclose(out, ref[rank * m:(rank + 1) * m].detach(), atol=1e-5)
+    out.square().sum().backward()
+    assert torch.allclose(xl.grad, xr.grad[rank * m:(rank + 1) * m], atol=1e-4)
+    w1r, w2r = w1.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+    (torch.tanh(x_all @ w1r.t()) @ w2r.t()).square().sum().backward()
+    assert torch.allclose(col.weight.grad, w1r.grad[rank * hl:(rank + 1) * hl], atol=1e-4)
+    assert torch.allclose(row.weight.grad, w2r.grad[:, rank * hl:(rank + 1) * hl], atol=1e-4)
+
+
+def test_sequence_parallel_linears_match_single_process():
+    run_ranks(_sequence_parallel_linears)
+
+
+# ------------------------------------------------------------------------------------------------
 def _pipeline(rank, world, schedule):
     from zenyx_b200.distributed import DistributedPipelineEngine, PipelineParallelModel
 

@@ -1,5 +1,5 @@
-"""Multi-GPU tests: fused ring attention (P2P pull / dK,dV push), fused sharded optimizer, and a
-DP x CP training run. Each spawns one process per GPU on this node with torch.distributed.run."""
+"""Multi-GPU tests: fused ring attention (P2P pull / dK,dV push), fused sharded optimizer, GEMMs fused
+with their all-gather / reduce-scatter, and a DP x CP training run. Each spawns one process per GPU on this node with torch.distributed.run."""
 import os
 import subprocess
 import sys
@@ -25,14 +25,14 @@ def _ngpu():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("case", ["ring", "zero", "train"])
+@pytest.mark.parametrize("case", ["ring", "zero", "train", "tp"])
 def test_two_gpus(case):
     out = _run(case, 2)
     assert f"{case} ok" in out
 
 
 @pytest.mark.skipif(_ngpu() < 4, reason="needs at least 4 GPUs")
-@pytest.mark.parametrize("case", ["ring", "train"])
+@pytest.mark.parametrize("case", ["ring", "train", "tp"])
 def test_four_gpus(case):
     out = _run(case, 4)
     assert f"{case} ok" in out

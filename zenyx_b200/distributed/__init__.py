@@ -8,7 +8,8 @@ from ..parallel.fsdp_wrapper import FSDPWrapper
 from ..parallel.groups import Mesh, ParallelLayout
 from ..parallel.pipeline_parallel import (DistributedPipelineEngine, Partial1F1BSchedule, PipelineParallelModel,
                                           PipelineStage, SimpleGPipeSchedule, create_pipeline_from_sequential)
-from ..parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear, TensorParallelEmbedding,
+from ..parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear, SequenceParallelColumnLinear,
+                                        SequenceParallelRowLinear, TensorParallelEmbedding,
                                         make_tensor_parallel_model)
 from ..parallel.zero import ZeroAdamW
 
@@ -18,5 +19,5 @@ __all__ = [
     "init_process_group", "reduce_scatter", "FSDPWrapper", "Mesh", "ParallelLayout", "DistributedPipelineEngine",
     "Partial1F1BSchedule", "PipelineParallelModel", "PipelineStage", "SimpleGPipeSchedule",
     "create_pipeline_from_sequential", "ColumnParallelLinear", "RowParallelLinear", "TensorParallelEmbedding",
-    "make_tensor_parallel_model", "ZeroAdamW",
+    "make_tensor_parallel_model", "ZeroAdamW", "SequenceParallelColumnLinear", "SequenceParallelRowLinear",
 ]

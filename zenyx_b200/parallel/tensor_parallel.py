@@ -167,6 +167,50 @@ class RowParallelLinear(nn.Module):
         return y + self.bias if self.bias is not None else y
 
 
+class SequenceParallelColumnLinear(nn.Module):
+    """Column-parallel linear whose INPUT is split by rows (tokens) over the group: the all-gather of
+    the tokens is fused into the GEMM (``parallel/fused_collective.py``); output [all tokens, local
+    features]. No counterpart in the reference, whose column-parallel layer takes a replicated
+    input (zenyx/distributed/tensor_parallel.py:29-58)."""
+
+    def __init__(self, in_features: int, out_features: int, group=None, device=None, dtype=torch.bfloat16,
+                 context=None):
+        super().__init__()
+        w = _world(group)
+        if out_features % w != 0:
+            raise ValueError("out_features must be divisible by the tensor-parallel degree")
+        self.group, self.context, self.local_out = group, context, out_features // w
+        self.weight = nn.Parameter(torch.empty(self.local_out, in_features, device=device, dtype=dtype))
+        nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        from .fused_collective import allgather_linear
+
+        return allgather_linear(x_local, self.weight, self.context, self.group)
+
+
+class SequenceParallelRowLinear(nn.Module):
+    """Row-parallel linear whose OUTPUT is split by rows (tokens): the partial products are
+    reduce-scattered by the GEMM epilogue itself (peer ``red.add``), see
+    ``parallel/fused_collective.py``. The reference's row-parallel layer all-reduces instead
+    (zenyx/distributed/tensor_parallel.py:61-116)."""
+
+    def __init__(self, in_features: int, out_features: int, group=None, device=None, dtype=torch.bfloat16,
+                 context=None):
+        super().__init__()
+        w = _world(group)
+        if in_features % w != 0:
+            raise ValueError("in_features must be divisible by the tensor-parallel degree")
+        self.group, self.context, self.local_in = group, context, in_features // w
+        self.weight = nn.Parameter(torch.empty(out_features, self.local_in, device=device, dtype=dtype))
+        nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from .fused_collective import linear_reduce_scatter
+
+        return linear_reduce_scatter(x, self.weight, self.context, self.group)
+
+
 class TensorParallelEmbedding(nn.Module):
     """Vocabulary-sharded embedding: local lookup with out-of-range ids masked, then all-reduce."""
 
