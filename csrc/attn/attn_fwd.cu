@@ -325,17 +325,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
         uint32_t pk[64];
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
+        // The row sum runs as two packed fp32x2 accumulators (two independent chains of 32 adds),
+        // the scale-and-shift as packed FMAs, and every fourth pair of exponentials on the FMA pipe.
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
         const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
         const float2 nm2 = make_float2(-m_used, -m_used);
-        for (int c = 0; c < 64; ++c) {   // packed fp32x2 FMA: two columns per instruction
+        auto softmax_pair = [&](auto idx) {
+          constexpr int c = decltype(idx)::value;
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2, nm2);
-          const float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
-          sum4[c & 3] += p0 + p1;
-          pk[c] = pack_bf16x2(p0, p1);
-        }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+          const float2 pe = exp2_pair<c>(x);
+          if (c & 1) sum_b = __fadd2_rn(sum_b, pe);
+          else sum_a = __fadd2_rn(sum_a, pe);
+          pk[c] = pack_bf16x2(pe.x, pe.y);
+        };
+        static_for<64>(softmax_pair);
+        l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
         tmem_st_32x32b_x32(s_tmem + 0, pk);
         tmem_st_32x32b_x32(s_tmem + 32, pk + 32);
         tmem_wait_st();

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <type_traits>
 #include "status.h"
 
 namespace zx {
@@ -419,6 +420,15 @@ __device__ __forceinline__ void warp_pull_slice(const uint4* __restrict__ src, u
   for (; i < end; i += 32) dst[i] = ld_stream_v4(src + i);
 }
 
+// Compile-time loop: f(std::integral_constant<int, i>) for i in [0, N).
+template <int N, int I = 0, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<N, I + 1>(f);
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
 // Small numeric helpers
 // ----------------------------------------------------------------------------------------------
@@ -434,6 +444,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^x for two values on the FMA pipe instead of the special-function unit. The unit produces 16
+// results per clock per SM, which is what bounds a softmax tile once the rest of the row's
+// arithmetic is packed; moving a quarter of the exponentials here balances the two pipes.
+// x = j + f with j = round(x), |f| <= 1/2; 2^f by a cubic fitted on [-1/2, 1/2] (relative error
+// below 8e-5, far inside the bf16 rounding the result gets) and j goes straight into the exponent
+// field. Inputs below -125 return (almost) zero.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));   // 1.5 * 2^23: round(x) lands in the mantissa
+  const float2 j = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __fadd2_rn(x, make_float2(-j.x, -j.y));
+  float2 q = __ffma2_rn(f, make_float2(0.05517166f, 0.05517166f), make_float2(0.24261113f, 0.24261113f));
+  q = __ffma2_rn(q, f, make_float2(0.69326097f, 0.69326097f));
+  q = __ffma2_rn(q, f, make_float2(0.99992806f, 0.99992806f));
+  return make_float2(__int_as_float((__float_as_int(t.x) << 23) + __float_as_int(q.x)),
+                     __int_as_float((__float_as_int(t.y) << 23) + __float_as_int(q.y)));
+}
+// Pair exponential; every fourth pair (by the caller's compile-time index) takes the FMA pipe.
+template <int kIndex>
+__device__ __forceinline__ float2 exp2_pair(float2 x) {
+  if ((kIndex & 3) == 3) return exp2_poly2(x);
+  return make_float2(fast_exp2(x.x), fast_exp2(x.y));
 }
 
 }  // namespace zx
