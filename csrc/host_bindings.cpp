@@ -5,6 +5,7 @@
 #include <pybind11/stl.h>
 
 #include "cpu_ref/flash_cpu.h"
+#include "peer/barrier_model.h"
 #include "tier/belady_min.h"
 #include "tier/tier_engine.h"
 
@@ -43,6 +44,20 @@ CpuAttnShape shape_of(const FArr& q, const FArr& k, float scale, bool causal, in
 }  // namespace
 
 PYBIND11_MODULE(_host, m) {
+  m.def("barrier_model", [](int ranks, int rounds, uint32_t start_epoch, uint64_t seed, int absent_rank,
+                            int absent_from_round, int64_t timeout_us) {
+    zx::BarrierModelResult r;
+    {
+      py::gil_scoped_release nogil;
+      r = zx::run_barrier_model(ranks, rounds, start_epoch, seed, absent_rank, absent_from_round, timeout_us);
+    }
+    py::dict d;
+    d["violations"] = r.violations;
+    d["timeouts"] = r.timeouts;
+    d["rounds_done"] = r.rounds_done;
+    return d;
+  }, py::arg("ranks"), py::arg("rounds"), py::arg("start_epoch") = 0, py::arg("seed") = 0, py::arg("absent_rank") = -1,
+     py::arg("absent_from_round") = 0, py::arg("timeout_us") = 2000000);
   m.def("belady_min", [](const std::vector<int64_t>& ids, const std::vector<int64_t>& size_of, int64_t cap) {
     for (auto id : ids)
       if (id < 0 || id >= (int64_t)size_of.size()) throw std::runtime_error("belady_min: block id out of range");

@@ -445,3 +445,103 @@ def test_peer_barrier_wait_is_bounded(C):
     finally:
         torch.cuda.synchronize()
         C.peer_free(flags)
+
+
+# ------------------------------------------------------------------------------------------------
+# Out-of-bounds and race detection without a sanitizer: guard bands and repeatability
+# ------------------------------------------------------------------------------------------------
+def _guarded(shape, dtype, fill, guard_elems=4096):
+    """A tensor of `shape` carved out of a larger buffer whose head and tail hold a known pattern."""
+    n = 1
+    for s in shape:
+        n *= s
+    buf = torch.full((n + 2 * guard_elems,), fill, device="cuda", dtype=dtype)
+    return buf, buf[guard_elems: guard_elems + n].view(*shape), guard_elems
+
+
+def _guards_intact(buf, guard, fill):
+    head, tail = buf[:guard], buf[-guard:]
+    ref = torch.full_like(head, fill)
+    return torch.equal(head.view(torch.int16 if buf.element_size() == 2 else torch.int32),
+                       ref.view(torch.int16 if buf.element_size() == 2 else torch.int32)) and \
+        torch.equal(tail.view(torch.int16 if buf.element_size() == 2 else torch.int32),
+                    ref.view(torch.int16 if buf.element_size() == 2 else torch.int32))
+
+
+def test_kernels_write_only_inside_their_outputs(C):
+    """Every output of the GEMM (ragged M and N), of the attention forward and of the attention backward
+    sits between guard bands filled with a pattern; the bands must come back untouched."""
+    torch.manual_seed(21)
+    M, N, K = 1000, 264, 520                       # ragged against the 128 x 256 x 64 tiles
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    gbuf, out, g = _guarded((M, N), torch.bfloat16, 77.0)
+    C.gemm(a, b, out, False, False, None)
+    _status_ok()
+    assert _guards_intact(gbuf, g, 77.0)
+    assert _rel_err(out, a.float() @ b.float().t()) < 1e-2
+    fbuf, outf, g = _guarded((M, N), torch.float32, 77.0)
+    outf.zero_()
+    C.gemm(a, b, outf, False, False, outf)          # fp32 accumulate-into-self (weight-gradient epilogue)
+    _status_ok()
+    assert _guards_intact(fbuf, g, 77.0)
+    B, S, Hq, Hkv, D = 1, 384, 4, 2, 128
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    obuf, o, g = _guarded((B, S, Hq, D), torch.bfloat16, 77.0)
+    lbuf, lse, _ = _guarded((B, Hq, S), torch.float32, 77.0)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_fwd(q, k, v, o, lse, scale, True, 0, 0, [0], [0], False, 0, 0, 0)
+    _status_ok()
+    assert _guards_intact(obuf, g, 77.0) and _guards_intact(lbuf, g, 77.0)
+    dbuf, delta, _ = _guarded((B, Hq, S), torch.float32, 77.0)
+    qbuf, dq, _ = _guarded((B, S, Hq, D), torch.float32, 77.0)
+    kbuf, dk, _ = _guarded((B, S, Hkv, D), torch.float32, 77.0)
+    vbuf, dv, _ = _guarded((B, S, Hkv, D), torch.float32, 77.0)
+    dk.zero_()
+    dv.zero_()
+    C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, True, 0, 0, [0], [0], True, False, 0, 0, 0)
+    _status_ok()
+    for buf in (dbuf, qbuf, kbuf, vbuf):
+        assert _guards_intact(buf, g, 77.0)
+    pos = torch.arange(S, device="cuda")
+    dq_r, dk_r, dv_r = _attn_bwd_ref(q, k, v, do, scale, pos, pos, True)
+    assert _rel_err(dq, dq_r) < 2e-2 and _rel_err(dk, dk_r) < 2e-2 and _rel_err(dv, dv_r) < 2e-2
+
+
+def test_kernels_are_repeatable(C):
+    """The same launch twice: GEMM, attention forward and dQ are deterministic and must match bit for
+    bit; dK/dV are accumulated with fp32 atomics across query heads and tiles, so they may differ in
+    the last bits only. A data race inside a kernel shows up here as a mismatch."""
+    torch.manual_seed(22)
+    a = torch.randn(1536, 1024, device="cuda").bfloat16()
+    b = torch.randn(2048, 1024, device="cuda").bfloat16()
+    outs = []
+    for _ in range(2):
+        o = torch.empty(1536, 2048, device="cuda", dtype=torch.bfloat16)
+        C.gemm(a, b, o, False, False, None)
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
+    B, S, Hq, Hkv, D = 1, 2048, 8, 2, 128
+    q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(D)
+    res = []
+    for _ in range(2):
+        o = torch.empty_like(q)
+        lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
+        C.attn_fwd(q, k, v, o, lse, scale, True, 0, 0, [0], [0], False, 0, 0, 0)
+        delta = torch.empty_like(lse)
+        dq = torch.empty(B, S, Hq, D, device="cuda")
+        dk = torch.zeros(B, S, Hkv, D, device="cuda")
+        dv = torch.zeros(B, S, Hkv, D, device="cuda")
+        C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, True, 0, 0, [0], [0], True, False, 0, 0, 0)
+        res.append((o, lse, dq, dk, dv))
+    _status_ok()
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert torch.equal(res[0][2], res[1][2])
+    assert _rel_err(res[0][3], res[1][3]) < 1e-5 and _rel_err(res[0][4], res[1][4]) < 1e-5

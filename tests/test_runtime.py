@@ -129,3 +129,20 @@ def test_memory_tracker_and_execution_plan():
     assert len(t.snapshots) == 4 and not t.possible_leak()
     p = ExecutionPlan.from_model(_mlp(), batch_size=2, seq_len=4)
     assert p.num_forward_ops == 3 and p.estimate_memory_gb() > 0 and p.estimate_time_seconds() > 0
+
+
+def test_peer_barrier_protocol_model_under_random_interleavings():
+    """The flag-barrier state machine of the peer barrier kernel, run on CPU threads with randomised
+    delays: nobody leaves a barrier before everyone entered it, data written before is visible after,
+    the epoch comparison survives the 32-bit wrap, and a missing rank ends the others' waits with a
+    time-out instead of a hang."""
+    from zenyx_b200.ops import _ext
+
+    h = _ext.host()
+    for seed in range(3):
+        r = h.barrier_model(4, 150, 0, seed)
+        assert r["violations"] == 0 and r["timeouts"] == 0 and r["rounds_done"] == 150, r
+    r = h.barrier_model(8, 80, 0xFFFFFFC0, 7)          # crosses the wrap of the 32-bit epoch
+    assert r["violations"] == 0 and r["timeouts"] == 0 and r["rounds_done"] == 80, r
+    r = h.barrier_model(3, 40, 0, 9, absent_rank=1, absent_from_round=10, timeout_us=20000)
+    assert r["violations"] == 0 and r["timeouts"] >= 1 and r["rounds_done"] == 10, r
