@@ -409,14 +409,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const int c = 2 * c4 + h;
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2,
                                         h == 0 ? make_float2(nl.x, nl.y) : make_float2(nl.z, nl.w));
-            float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
-            if (diag) {
-              if (my_kpos > qp + 2 * c) p0 = 0.f;
-              if (my_kpos > qp + 2 * c + 1) p1 = 0.f;
-            }
-            sr[2 * c] = __float_as_uint(p0);
-            sr[2 * c + 1] = __float_as_uint(p1);
+            sr[2 * c] = __float_as_uint(fast_exp2(x.x));
+            sr[2 * c + 1] = __float_as_uint(fast_exp2(x.y));
           }
+        }
+        if (diag) {   // only tiles on the diagonal pay for the per-element mask
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (my_kpos > qp + c) sr[c] = 0u;
         }
         ZX_TRACE_W(n, 2);
         {
@@ -713,13 +713,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int c = 0; c < 32; ++c) {   // packed fp32x2 math: two key columns per instruction
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2, nl2);
-          float p0 = fast_exp2(x.x), p1 = fast_exp2(x.y);
-          if (diag) {
-            if (kp + 2 * c > my_qpos) p0 = 0.f;
-            if (kp + 2 * c + 1 > my_qpos) p1 = 0.f;
-          }
-          sr[2 * c] = __float_as_uint(p0);
-          sr[2 * c + 1] = __float_as_uint(p1);
+          sr[2 * c] = __float_as_uint(fast_exp2(x.x));
+          sr[2 * c + 1] = __float_as_uint(fast_exp2(x.y));
+        }
+        if (diag) {   // only tiles on the diagonal pay for the per-element mask
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (kp + c > my_qpos) sr[c] = 0u;
         }
         if (threadIdx.x == 0) ZX_TRACE(n, 2);
         if (threadIdx.x == 160) ZX_TRACE(n, 12);

@@ -198,20 +198,30 @@ class BeladyKVCacheTieringManager:
             return self._plan
         ids = self._seq.block_ids(self.rank)
         n_blocks = self.num_layers * self.blocks_per_layer
-        res = _ext.host().belady_min(ids, [self.block_bytes] * n_blocks, self.hbm_budget_bytes)
+        res = _ext.host().belady_min(ids, [self.block_bytes] * n_blocks, self.plan_capacity_bytes())
         self._plan = TierPlan(ids=ids, hit=[bool(h) for h in res["hit"]], evict_before=[list(e) for e in res["evicted"]],
                               next_use=[int(x) for x in res["next_use"]], hits=int(res["hits"]),
                               misses=int(res["misses"]), bytes_loaded=int(res["bytes_loaded"]),
                               bytes_evicted=int(res["bytes_evicted"]),
                               peak_resident_bytes=int(res["peak_resident_bytes"]), bypassed=int(res["bypassed"]),
-                              block_bytes=self.block_bytes, capacity_bytes=self.hbm_budget_bytes)
+                              block_bytes=self.block_bytes, capacity_bytes=self.plan_capacity_bytes())
         return self._plan
 
+    def plan_capacity_bytes(self) -> int:
+        """HBM bytes the residency plan may fill. When the KV spills, ``lookahead`` blocks of the budget
+        are held back from the plan so that prefetches of the next foreseen misses always find room
+        (a plan that fills the budget to the last block turns every miss into a demand load)."""
+        if self.total_kv_bytes() <= self.hbm_budget_bytes:
+            return self.hbm_budget_bytes
+        slots = self.hbm_budget_bytes // self.block_bytes
+        spare = min(self.lookahead, max(1, slots // 8), max(0, slots - 1)) * self.block_bytes
+        return max(self.block_bytes, self.hbm_budget_bytes - spare)
+
     def lru_baseline(self) -> Dict[str, int]:
-        """The same trace under LRU (what the reference's host tier does), for comparison."""
+        """The same trace under LRU at the same usable capacity (what the reference's host tier does)."""
         ids = self._seq.block_ids(self.rank)
         res = _ext.host().lru_trace(ids, [self.block_bytes] * (self.num_layers * self.blocks_per_layer),
-                                    self.hbm_budget_bytes)
+                                    self.plan_capacity_bytes())
         return {"hits": int(res["hits"]), "misses": int(res["misses"]), "bytes_loaded": int(res["bytes_loaded"])}
 
     def total_kv_bytes(self) -> int:
