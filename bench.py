@@ -200,6 +200,9 @@ def run_ours(args):
         out["config"]["peaks"] = pk.source
     except Exception:  # noqa: BLE001
         pass
+    free_b, total_b = torch.cuda.mem_get_info()
+    out["config"]["peak_torch_alloc_gb"] = round(torch.cuda.max_memory_allocated() / 1e9, 1)
+    out["config"]["device_mem_used_gb"] = round((total_b - free_b) / 1e9, 1)   # includes peer buffers and the context
     if rank == 0:
         print(json.dumps(out), flush=True)
     trainer.close()
