@@ -480,7 +480,9 @@ void zero_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>
     TORCH_CHECK(g_shard->scalar_type() == torch::kFloat32 && g_shard->numel() >= n_shard, "zero_step: g_shard");
     a.g_shard = g_shard->data_ptr<float>();
   } else {
-    TORCH_CHECK(do_reduce && do_update, "zero_step: split passes need a g_shard buffer");
+    // without a shard buffer a pass either updates straight from the reduced gradients, or (norm pass)
+    // only accumulates their sum of squares and leaves them in place for a second reducing pass
+    TORCH_CHECK(do_reduce && (do_update || !zero_grads), "zero_step: this pass needs a g_shard buffer");
   }
   a.p_lo = reinterpret_cast<int16_t*>(p_lo.data_ptr());
   a.m = m.data_ptr<float>();

@@ -91,48 +91,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #define ZX_WAIT_LIMIT_NS 2000000000ull
 #endif
 
-#ifndef ZX_WAIT_MODE
-#define ZX_WAIT_MODE 0
-#define ZX_WAIT_HINT 0
-#endif
 // Bounded wait. Returns false when the wait gave up (its own limit, or another role already
 // raised *abort). The caller must then fall through to the kernel's teardown.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
-#if ZX_WAIT_MODE == 0
   for (int i = 0; i < 1024; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
-#elif ZX_WAIT_MODE == 1
-  for (int i = 0; i < 100000; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)ZX_WAIT_HINT)
-        : "memory");
-    if (ok) return true;
-  }
-#else
-  for (int i = 0; i < 100000; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    __nanosleep(ZX_WAIT_HINT);
-  }
-#endif
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {

@@ -60,8 +60,8 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
       }
       g.x *= p.grad_scale; g.y *= p.grad_scale; g.z *= p.grad_scale; g.w *= p.grad_scale;
       local_ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
-      if (!p.do_update) {
-        reinterpret_cast<float4*>(p.g_shard)[i] = g;
+      if (!p.do_update) {   // norm pass: keep the reduced shard if there is room for it, else only its norm
+        if (p.g_shard != nullptr) reinterpret_cast<float4*>(p.g_shard)[i] = g;
         continue;
       }
     } else {

@@ -45,7 +45,12 @@ class ZeroAdamW:
         self.step_count = 0
         self.on_gpu = dev.type == "cuda"
         self.fused_peer = fused_peer and self.on_gpu and (self.world == 1 or flat.sym_grads is not None)
-        need_gshard = (max_grad_norm is not None) or not self.fused_peer
+        # Clipping needs the global norm before the update. With several ranks the reduced shard is kept
+        # between the two passes (re-reading every peer's gradients would double the NVLink traffic); on a
+        # single GPU the second pass simply reads the gradient buffer again, which saves 4 bytes per
+        # parameter (32 GB for the 8B model) for activations.
+        self.rereduce = self.fused_peer and self.world == 1
+        need_gshard = ((max_grad_norm is not None) and not self.rereduce) or not self.fused_peer
         self.g_shard = torch.zeros(self.n_shard, device=dev, dtype=torch.float32) if need_gshard else None
         self.sumsq = torch.zeros(1, device=dev, dtype=torch.float32)
         self.clip = torch.ones(1, device=dev, dtype=torch.float32)
@@ -78,20 +83,25 @@ class ZeroAdamW:
             common = dict(grad_scale=grad_scale, lr=lr, beta1=b1, beta2=b2, eps=self.eps,
                           weight_decay=self.weight_decay, step=self.step_count)
 
-            def launch(do_reduce, do_update, clip):
+            def launch(do_reduce, do_update, clip, zero_grads=None, want_norm=None):
+                zero_grads = do_reduce if zero_grads is None else zero_grads
+                want_norm = do_reduce if want_norm is None else want_norm
                 C.zero_step(self.grad_ptrs, self.param_ptrs, rank_arg, self.shard_begin, self.n_shard,
                             self.flat.decay_end, self.g_shard, self.p_lo, self.m, self.v,
-                            self.sumsq if do_reduce else None, clip, do_reduce, do_update, do_reduce,
+                            self.sumsq if want_norm else None, clip, do_reduce, do_update, zero_grads,
                             common["grad_scale"], common["lr"], common["beta1"], common["beta2"], common["eps"],
                             common["weight_decay"], common["step"])
 
             if clipping:
                 self.sumsq.zero_()
-                launch(True, False, None)
+                launch(True, False, None, zero_grads=not self.rereduce)
                 if self.world > 1:
                     dist.all_reduce(self.sumsq, group=self.group)
                 fused.clip_coef_(self.sumsq, 1.0, float(self.max_grad_norm), self.clip, self.grad_norm)
-                launch(False, True, self.clip)
+                if self.rereduce:
+                    launch(True, True, self.clip, zero_grads=True, want_norm=False)
+                else:
+                    launch(False, True, self.clip)
             else:
                 launch(True, True, None)
             if self.barrier is not None:

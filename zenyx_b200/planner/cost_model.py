@@ -56,6 +56,8 @@ def estimate(cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, cp:
     micro_batches = max(1, global_batch // dp)
     # parameters bf16 + fp32 gradient buffer are replicated; master remainder + m + v are sharded
     state = P * (2 + 4) + P * (2 + 4 + 4) / (n_gpus if zero_shard else 1)
+    if n_gpus > 1:
+        state += P * 4 / n_gpus   # the reduced fp32 gradient shard kept between the norm pass and the update
     act = remat.bytes_per_token_per_layer(cfg) * tokens_rank * cfg.n_layers
     # live set of one layer's forward/backward (gate|up, its gradient, qkv, fp32 dq/dk/dv) + one logits chunk
     per_tok = 2 * (2 * 2 * cfg.ffn_dim + 2 * cfg.ffn_dim + 2 * cfg.qkv_dim + 4 * cfg.d_model) + 4 * cfg.qkv_dim

@@ -53,7 +53,12 @@ class LlamaEngine:
         if remat is None:
             from ..planner import plan
 
-            remat = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=max(degrees)).remat
+            kw = {}
+            if self.ctx.device.type == "cuda":   # size the plan for the memory this GPU really has
+                import torch
+
+                kw = {"hbm_bytes": float(torch.cuda.mem_get_info(self.ctx.device)[1]), "memory_fraction": 0.93}
+            remat = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=max(degrees), **kw).remat
         dev = self.ctx.device
         sym_group = dist.group.WORLD if (world > 1 and dev.type == "cuda" and cfg.fused_peer) else None
         self.model = LlamaModel(model_cfg, device=dev, remat=remat, seed=cfg.seed, symmetric_group=sym_group,
