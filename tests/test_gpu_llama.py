@@ -15,7 +15,7 @@ def _models(policy):
     return cfg, gpu, cpu
 
 
-@pytest.mark.parametrize("policy_name", ["selective", "none", "full"])
+@pytest.mark.parametrize("policy_name", ["selective", "none", "full", "host_offload"])
 def test_llama_gpu_matches_cpu_fp32(policy_name):
     from zenyx_b200.models import RematPolicy
     from zenyx_b200.ops import _ext
@@ -26,6 +26,10 @@ def test_llama_gpu_matches_cpu_fp32(policy_name):
     targets = torch.randint(0, cfg.vocab_size, (2, 512))
     l_cpu = cpu.forward_backward(tokens, targets)
     l_gpu = gpu.forward_backward(tokens.cuda(), targets.cuda())
+    if policy_name == "host_offload":   # a second micro-batch reuses the pinned buffers and staging slots
+        l_cpu = cpu.forward_backward(tokens, targets)
+        l_gpu = gpu.forward_backward(tokens.cuda(), targets.cuda())
+        assert len(gpu._off_host) == cfg.n_layers and all(t.is_pinned() for t in gpu._off_host.values())
     _ext.check_status()
     assert abs(l_cpu.item() - l_gpu.item()) < 3e-2
     for name in ["layers.0.wqkv", "layers.1.wd", "layers.0.wgu", "layers.1.wo", "lm_head.weight", "embed.weight",

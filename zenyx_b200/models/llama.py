@@ -80,7 +80,10 @@ class RematPolicy:
     """Which per-layer activations are kept for backward; the rest is recomputed.
 
     Names: ``x`` (layer input, always kept), ``attn`` (attention output + log-sum-exp), ``qkv``
-    (rotated Q/K/V), ``h1`` (post-attention residual stream), ``gu`` (gate|up projection).
+    (rotated Q/K/V), ``h1`` (post-attention residual stream), ``gu`` (gate|up projection),
+    ``gu@host`` (gate|up projection kept in pinned host memory: copied out on a side stream while the
+    layer's forward continues, prefetched one layer ahead during backward; costs no HBM beyond two
+    staging buffers and replaces the largest recomputed GEMM of a layer by two PCIe copies).
     """
 
     saved: Tuple[str, ...] = ("x", "attn")
@@ -97,9 +100,16 @@ class RematPolicy:
     def none(cls) -> "RematPolicy":        # keep everything a GEMM or the attention produced
         return cls(("x", "attn", "qkv", "h1", "gu"))
 
+    @classmethod
+    def host_offload(cls) -> "RematPolicy":   # everything small in HBM, gate|up in pinned host memory
+        return cls(("x", "attn", "qkv", "h1", "gu@host"))
+
+    def host_bytes_per_token_per_layer(self, cfg: LlamaConfig) -> int:
+        return 2 * 2 * cfg.ffn_dim if "gu@host" in self.saved else 0
+
     def bytes_per_token_per_layer(self, cfg: LlamaConfig) -> int:
         sizes = {"x": cfg.d_model, "attn": cfg.n_heads * cfg.head_dim + 2 * cfg.n_heads, "qkv": cfg.qkv_dim,
-                 "h1": cfg.d_model, "gu": 2 * cfg.ffn_dim}
+                 "h1": cfg.d_model, "gu": 2 * cfg.ffn_dim, "gu@host": 0}
         return 2 * sum(sizes[n] for n in self.saved)
 
 
@@ -188,6 +198,12 @@ class LlamaModel(nn.Module):
             param.main_grad = self.flat.grad(name)
             self.register_parameter(name.replace(".", "_"), param)
         self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+        # host offload of gate|up activations (RematPolicy name "gu@host")
+        self._off_stream = None
+        self._off_host: Dict[int, torch.Tensor] = {}
+        self._off_stage: List[torch.Tensor] = []
+        self._off_ready: Dict[int, "torch.cuda.Event"] = {}
+        self._off_stage_free: List[Optional["torch.cuda.Event"]] = [None, None]
 
     # -------------------------------------------------------------------------------------------
     def w(self, name: str) -> torch.Tensor:
@@ -205,6 +221,53 @@ class LlamaModel(nn.Module):
 
     def zero_grad(self, set_to_none: bool = False) -> None:  # noqa: ARG002
         self.flat.grads.zero_()
+
+    # -------------------------------------------------------------------------------------------
+    # gate|up activations in pinned host memory
+    # -------------------------------------------------------------------------------------------
+    def _offload_gu(self, l: int, gu: torch.Tensor) -> None:
+        """Starts the device-to-host copy of layer l's gate|up activation on the side stream."""
+        if self._off_stream is None:
+            self._off_stream = torch.cuda.Stream()
+        host = self._off_host.get(l)
+        if host is None or host.shape != gu.shape:
+            host = torch.empty(gu.shape, dtype=gu.dtype, pin_memory=True)
+            self._off_host[l] = host
+        main = torch.cuda.current_stream()
+        self._off_stream.wait_stream(main)              # gu has been produced
+        with torch.cuda.stream(self._off_stream):
+            host.copy_(gu, non_blocking=True)
+        gu.record_stream(self._off_stream)              # its memory is not reused before the copy has read it
+
+    def _start_fetch_gu(self, l: int) -> None:
+        """Starts the host-to-device copy of layer l's gate|up activation into a staging buffer."""
+        if l < 0 or l in self._off_ready or l not in self._off_host:
+            return
+        host = self._off_host[l]
+        slot = l % 2
+        if len(self._off_stage) < 2:
+            self._off_stage = [torch.empty(host.shape, dtype=host.dtype, device="cuda") for _ in range(2)]
+        with torch.cuda.stream(self._off_stream):
+            if self._off_stage_free[slot] is not None:
+                self._off_stream.wait_event(self._off_stage_free[slot])   # the previous user of the slot is done
+            self._off_stage[slot].view(-1)[: host.numel()].view(host.shape).copy_(host, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        self._off_ready[l] = ev
+
+    def _fetch_gu(self, l: int) -> torch.Tensor:
+        """Layer l's gate|up activation on the device; also starts the fetch for layer l - 1."""
+        self._start_fetch_gu(l)
+        torch.cuda.current_stream().wait_event(self._off_ready.pop(l))
+        host = self._off_host[l]
+        gu = self._off_stage[l % 2].view(-1)[: host.numel()].view(host.shape)
+        self._start_fetch_gu(l - 1)
+        return gu
+
+    def _release_gu(self, l: int) -> None:
+        ev = torch.cuda.Event()
+        ev.record()
+        self._off_stage_free[l % 2] = ev
 
     def _rope(self, ring: RingContext, s_local: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
         key = (ring.rank, ring.degree, ring.seq_len, ring.layout, s_local, str(device))
@@ -262,6 +325,9 @@ class LlamaModel(nn.Module):
                 saved["h1"] = h1
             if "gu" in names:
                 saved["gu"] = gu
+            elif "gu@host" in names and gu.is_cuda:
+                self._offload_gu(l, gu)
+                saved["gu_host"] = True
         return out, saved
 
     def _layer_backward(self, l: int, dout, saved, B: int, S: int, ring: RingContext):
@@ -291,7 +357,12 @@ class LlamaModel(nn.Module):
             o, lse = ring_attn_forward(ring, q, k, v, scale, slot=l % 2)
         h1 = saved["h1"] if "h1" in saved else gemm(o.view(T, -1), self.w(pre + "wo"), addend=x)
         hn, rstd2 = fused.rmsnorm_fwd(h1, self.w(pre + "norm2"), cfg.norm_eps)
-        gu = saved["gu"] if "gu" in saved else gemm(hn, self.w(pre + "wgu"))
+        if "gu" in saved:
+            gu = saved["gu"]
+        elif "gu_host" in saved:
+            gu = self._fetch_gu(l)
+        else:
+            gu = gemm(hn, self.w(pre + "wgu"))
         a = fused.swiglu_fwd(gu)
         # ---- FFN backward ----
         gwd, gwgu = self.g(pre + "wd"), self.g(pre + "wgu")
@@ -299,6 +370,8 @@ class LlamaModel(nn.Module):
         gemm(dout, a, trans_a=True, trans_b=True, out=gwd, addend=gwd)
         del a
         dgu = fused.swiglu_bwd(gu, da)
+        if "gu_host" in saved:
+            self._release_gu(l)   # the staging slot may take the activation of layer l - 2 now
         del da, gu
         dhn = gemm(dgu, self.w(pre + "wgu"), trans_b=True)
         gemm(dgu, hn, trans_a=True, trans_b=True, out=gwgu, addend=gwgu)
@@ -372,6 +445,8 @@ class LlamaModel(nn.Module):
             for l in range(self.cfg.n_layers):
                 h, saved = self._layer_forward(l, h, B, S, ring, keep=True)
                 saved_all.append(saved)
+            if "gu@host" in self.remat.saved and h.is_cuda:
+                self._start_fetch_gu(self.cfg.n_layers - 1)   # under the LM head instead of in front of the last layer
             loss, dh = self._head_loss(h, targets, loss_weight, want_grad=True)
             del h
             for l in reversed(range(self.cfg.n_layers)):

@@ -62,6 +62,8 @@ def estimate(cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, cp:
     # live set of one layer's forward/backward (gate|up, its gradient, qkv, fp32 dq/dk/dv) + one logits chunk
     per_tok = 2 * (2 * 2 * cfg.ffn_dim + 2 * cfg.ffn_dim + 2 * cfg.qkv_dim + 4 * cfg.d_model) + 4 * cfg.qkv_dim
     work = per_tok * tokens_rank + 2 * 4096 * cfg.vocab_size * 2
+    if "gu@host" in remat.saved:
+        work += 2 * (2 * 2 * cfg.ffn_dim) * tokens_rank   # two device staging buffers for the host-resident gate|up
     flops_tok = cfg.flops_per_token(seq_len)
     recompute = 0.0
     per_layer_mm = 2.0 * (cfg.qkv_dim + cfg.n_heads * cfg.head_dim + 3 * cfg.ffn_dim) * cfg.d_model
@@ -69,7 +71,7 @@ def estimate(cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, cp:
         recompute += 2.0 * cfg.qkv_dim * cfg.d_model
     if "h1" not in remat.saved:
         recompute += 2.0 * cfg.n_heads * cfg.head_dim * cfg.d_model
-    if "gu" not in remat.saved:
+    if "gu" not in remat.saved and "gu@host" not in remat.saved:
         recompute += 2.0 * 2 * cfg.ffn_dim * cfg.d_model
     if "attn" not in remat.saved:
         recompute += 4.0 * seq_len * cfg.head_dim * cfg.n_heads * 0.5

@@ -13,8 +13,23 @@ from typing import List, Optional, Sequence
 from ..models.llama import LlamaConfig, RematPolicy
 from .cost_model import HardwarePeaks, StepEstimate, estimate
 
-REMAT_LADDER = [RematPolicy.none(), RematPolicy(("x", "attn", "h1", "qkv")), RematPolicy(("x", "attn", "h1")),
-                RematPolicy.selective(), RematPolicy.full()]
+# Host offload of the gate|up activation (RematPolicy.host_offload) is deliberately NOT on the ladder: on the
+# B200 boxes this was measured on, the 120 GB per micro-batch it moves over PCIe ran at about 26 GB/s and
+# made the 8B / 32K step 1.47x slower than recomputing the GEMM. It stays available as an explicit policy.
+REMAT_LADDER = [RematPolicy.none(), RematPolicy(("x", "attn", "h1", "qkv")),
+                RematPolicy(("x", "attn", "h1")), RematPolicy.selective(), RematPolicy.full()]
+
+
+def host_memory_available_bytes() -> float:
+    """MemAvailable of this machine (0 when it cannot be read)."""
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return float(line.split()[1]) * 1024.0
+    except OSError:
+        pass
+    return 0.0
 
 
 @dataclass
@@ -39,7 +54,8 @@ class ParallelPlan:
 
 def plan(model_cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, hbm_bytes: float = 180e9,
          nvlink_GBps: float = 770.0, ring_degree: Optional[int] = None, candidates: Sequence[int] = (1, 2, 4, 8),
-         memory_fraction: float = 0.88, peaks: Optional[HardwarePeaks] = None) -> ParallelPlan:
+         memory_fraction: float = 0.88, peaks: Optional[HardwarePeaks] = None,
+         host_bytes: Optional[float] = None) -> ParallelPlan:
     """Returns the fastest plan whose estimated footprint fits in ``memory_fraction * hbm_bytes``.
 
     With ``ring_degree`` given only the rematerialisation policy is searched (the benchmark configs
@@ -59,6 +75,11 @@ def plan(model_cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, h
         for remat in REMAT_LADDER:
             est = estimate(model_cfg, seq_len, global_batch, n_gpus, cp, remat, peaks)
             if est.total_bytes > budget:
+                continue
+            # pinned host memory for offloaded activations: every rank of the node needs its own, and half of
+            # what the machine has free stays untouched
+            need_host = remat.host_bytes_per_token_per_layer(model_cfg) * (seq_len // cp) * model_cfg.n_layers * n_gpus
+            if need_host > 0.5 * (host_memory_available_bytes() if host_bytes is None else host_bytes):
                 continue
             cand = ParallelPlan(dp=dp, cp=cp, micro_batch=1, micro_batches=global_batch // dp, remat=remat,
                                 kv_budget_bytes=int(min(16 << 30, 0.1 * hbm_bytes)), estimate=est)
