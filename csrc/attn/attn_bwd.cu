@@ -16,6 +16,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tma_host.h"
 #include "attn.h"
+#include "tile_iter.cuh"
 
 namespace zx {
 
@@ -223,8 +224,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   // number of (head, q tile) items this CTA processes: identical in every role
   int n_items = 0;
-  for (int t = 0; t < p.n_q_tiles; ++t)
-    if (tile_allowed(p, q_tile_pos(p, t), kpos0)) ++n_items;
+  for (int t = next_q_tile(p, kpos0, 0); t < p.n_q_tiles; t = next_q_tile(p, kpos0, t + 1)) ++n_items;
   n_items *= G;
 
   if (warp == KW_PULL) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
@@ -244,8 +244,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         bool ok = true;
         for (int g = 0; g < G && ok; ++g) {
           const int hq = hk * G + g;
-          for (int t = 0; t < p.n_q_tiles; ++t) {
-            if (!tile_allowed(p, q_tile_pos(p, t), kpos0)) continue;
+          for (int t = next_q_tile(p, kpos0, 0); t < p.n_q_tiles; t = next_q_tile(p, kpos0, t + 1)) {
             const int qs = n % Q_STAGES, ds = n % DO_STAGES;
             if (!mbar_wait(&q_empty[qs], ((n / Q_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
             mbar_expect_tx(&q_full[qs], TILE_BYTES);
@@ -367,11 +366,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       };
       auto next_item = [&](int& g, int& t) -> bool {
         for (;;) {
-          if (++t >= p.n_q_tiles) {
-            t = 0;
-            if (++g >= G) return false;
-          }
-          if (tile_allowed(p, q_tile_pos(p, t), kpos0)) return true;
+          t = next_q_tile(p, kpos0, t + 1);
+          if (t < p.n_q_tiles) return true;
+          t = -1;
+          if (++g >= G) return false;
         }
       };
       int g = 0, t = -1;
@@ -580,8 +578,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   int n_items = 0;
-  for (int j = 0; j < p.n_kv_tiles; ++j)
-    if (tile_allowed(p, qpos0, kv_tile_pos(p, j))) ++n_items;
+  for (int j = next_kv_tile(p, qpos0, 0); j < p.n_kv_tiles; j = next_kv_tile(p, qpos0, j + 1)) ++n_items;
 
   if (n_items > 0) {
     if (warp == W_TMA) {
@@ -595,8 +592,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_4d(sdO + HALF_BYTES, &tmdO, qdo_full, 64, hq, t * BT, b);
         uint32_t n = 0;
         bool ok = true;
-        for (int j = 0; j < p.n_kv_tiles; ++j) {
-          if (!tile_allowed(p, qpos0, kv_tile_pos(p, j))) continue;
+        for (int j = next_kv_tile(p, qpos0, 0); j < p.n_kv_tiles; j = next_kv_tile(p, qpos0, j + 1)) {
           const int ks = n % K_STAGES, vs = n % V_STAGES;
           if (!mbar_wait(&k_empty[ks], ((n / K_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&k_full[ks], TILE_BYTES);
@@ -692,9 +688,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int my_qpos = qpos0 + r;
       uint32_t n = 0;
       bool ok = true;
-      for (int j = 0; j < p.n_kv_tiles; ++j) {
+      for (int j = next_kv_tile(p, qpos0, 0); j < p.n_kv_tiles; j = next_kv_tile(p, qpos0, j + 1)) {
         const int kpos0 = kv_tile_pos(p, j);
-        if (!tile_allowed(p, qpos0, kpos0)) continue;
         if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (threadIdx.x == 0) ZX_TRACE(n, 0);

@@ -70,7 +70,7 @@ def _digest(paths) -> str:
 
 def _deps(src: Path):
     """The source plus every header under csrc/ (coarse but safe)."""
-    return [src] + sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh"))
+    return [src] + sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh")) + sorted(CSRC.rglob("*.inc"))
 
 
 def _run(cmd, verbose):
