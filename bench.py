@@ -35,7 +35,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--global-batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers makes the number invalid")
-    ap.add_argument("--ring-degree", type=int, default=0, help="context-parallel degree (default: all GPUs)")
+    ap.add_argument("--ring-degree", type=int, default=0, help="context-parallel degree (default: the planner chooses dp x cp)")
     ap.add_argument("--no-fused-peer", action="store_true", help="NCCL reduce-scatter/all-gather optimizer path")
     ap.add_argument("--remat", default="auto", choices=["auto", "full", "selective", "none"])
     ap.add_argument("--skip-e2e", action="store_true")
@@ -106,9 +106,15 @@ def run_ours(args):
     ctx = init_distributed_from_env()
     world, rank = ctx.world_size, ctx.rank
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    cp = args.ring_degree or world
     mc = LlamaConfig.llama3_8b()
     mc.n_layers = args.layers
+    if args.ring_degree:
+        cp = args.ring_degree
+    else:   # let the planner split the GPUs into data-parallel replicas x context-parallel ring
+        from zenyx_b200.planner import plan
+
+        cp = plan(mc, args.seq_len, args.global_batch, world, hbm_bytes=float(torch.cuda.mem_get_info()[1]),
+                  memory_fraction=0.93).cp
     remat = {"auto": None, "full": RematPolicy.full(), "selective": RematPolicy.selective(),
              "none": RematPolicy.none()}[args.remat]
     tcfg = TrainerConfig(lr=3e-4, seq_len=args.seq_len, global_batch=args.global_batch, ring_degree=cp,
