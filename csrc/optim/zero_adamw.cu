@@ -39,6 +39,9 @@ __device__ __forceinline__ float4 ld_f4_stream(const float* p) {
   return v;
 }
 
+// NR: number of ranks known at compile time (1, 2, 4, 8), so the peer loads of one element are all in
+// flight together instead of one NVLink round trip after another; 0 = any count, loop at run time.
+template <int NR>
 __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
   __shared__ float s_red[8];
   const size_t nvec = p.n_shard >> 2;
@@ -50,13 +53,31 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
     if (p.do_reduce) {
       g = make_float4(0.f, 0.f, 0.f, 0.f);
       // start with the next rank so the R readers of one step hit R different owners
-      for (int k = 0; k < p.nranks; ++k) {
-        int r = p.rank + 1 + k;
-        if (r >= p.nranks) r -= p.nranks;
-        float* src = reinterpret_cast<float*>(p.grads.p[r]) + gi;
-        const float4 a = ld_f4_stream(src);
-        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-        if (p.zero_grads) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if constexpr (NR > 0) {
+        float* src[NR];
+        float4 a[NR];
+#pragma unroll
+        for (int k = 0; k < NR; ++k) {
+          int r = p.rank + 1 + k;
+          if (r >= NR) r -= NR;
+          src[k] = reinterpret_cast<float*>(p.grads.p[r]) + gi;
+        }
+#pragma unroll
+        for (int k = 0; k < NR; ++k) a[k] = ld_f4_stream(src[k]);
+#pragma unroll
+        for (int k = 0; k < NR; ++k) {
+          g.x += a[k].x; g.y += a[k].y; g.z += a[k].z; g.w += a[k].w;
+          if (p.zero_grads) *reinterpret_cast<float4*>(src[k]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      } else {
+        for (int k = 0; k < p.nranks; ++k) {
+          int r = p.rank + 1 + k;
+          if (r >= p.nranks) r -= p.nranks;
+          float* src = reinterpret_cast<float*>(p.grads.p[r]) + gi;
+          const float4 a = ld_f4_stream(src);
+          g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+          if (p.zero_grads) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
       g.x *= p.grad_scale; g.y *= p.grad_scale; g.z *= p.grad_scale; g.w *= p.grad_scale;
       local_ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
@@ -132,7 +153,13 @@ void launch_zero_step(const ZeroArgs& a) {
   size_t blocks = (nvec + 255) / 256;
   const size_t cap = (size_t)a.sm_count * 8;
   if (blocks > cap) blocks = cap;
-  zero_step_kernel<<<(unsigned)blocks, 256, 0, a.stream>>>(p);
+  switch (a.nranks) {
+    case 1: zero_step_kernel<1><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
+    case 2: zero_step_kernel<2><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
+    case 4: zero_step_kernel<4><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
+    case 8: zero_step_kernel<8><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
+    default: zero_step_kernel<0><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
+  }
 }
 
 }  // namespace zx
