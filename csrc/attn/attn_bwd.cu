@@ -29,7 +29,7 @@ constexpr int BT = 128;                    // tile edge in tokens (both Q and KV
 constexpr int TILE_BYTES = BT * HD * 2;    // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk
 constexpr int NUM_THREADS = 320;           // 8 compute warps (two warpgroups) + TMA warp + MMA warp
-constexpr int W_TMA = 8, W_MMA = 9, W_PULL = 10;
+constexpr int W_TMA = 8, W_MMA = 9;        // dQ kernel roles (the dK/dV kernel has its own, below)
 constexpr int N_COMPUTE = 256;             // compute threads
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -70,17 +70,6 @@ struct BwdParams {
     if (p.trace != nullptr && blockIdx.x == 0 && (iter) < 64) p.trace[(iter) * 16 + (slot)] = clock64(); \
   } while (0)
 
-__device__ __forceinline__ bool tile_allowed(const BwdParams& p, int qpos0, int kpos0) {
-  if (p.causal && kpos0 > qpos0) return false;
-  if (p.window_blocks > 0) {
-    const int qb = qpos0 >> 7, kb = kpos0 >> 7;
-    const int dist = qb >= kb ? qb - kb : kb - qb;
-    const bool in_window = dist < p.window_blocks;
-    const bool is_global = p.global_every > 0 && (kb % p.global_every) == 0;
-    if (!in_window && !is_global) return false;
-  }
-  return true;
-}
 __device__ __forceinline__ int q_tile_pos(const BwdParams& p, int t) {
   return p.q_chunk_pos[t / p.q_tiles_per_chunk] + (t % p.q_tiles_per_chunk) * BT;
 }

@@ -78,6 +78,7 @@ def main(argv=None):
     ms = min(times)
     print(json.dumps({
         "metric": "KV tiering stress step time", "value": round(ms, 2), "unit": "ms", "higher_is_better": False,
+        "step_ms_all": [round(t, 2) for t in times],
         "context_tokens": args.context, "ring": args.ring, "layers": args.layers, "block_tokens": bt,
         "share_kv_bytes": mgr.total_kv_bytes(), "hbm_budget_bytes": mgr.hbm_budget_bytes, "accesses_per_step": n_acc,
         "plan": {"hits": plan.hits, "misses": plan.misses, "hit_rate": round(plan.hit_rate, 4), "lru_misses": lru["misses"],

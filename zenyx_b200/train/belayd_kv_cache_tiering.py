@@ -184,7 +184,13 @@ class BeladyKVCacheTieringManager:
         self._cursor = 0
         self._copy_stream = None
         self._file = None
-        self._bounce: Optional[torch.Tensor] = None
+        self._bounce: Optional[torch.Tensor] = None   # pinned staging buffer for writes to the file tier
+        # reads from the file tier are asynchronous: a pool of pinned buffers, a worker-thread read per
+        # prefetched block, and the host-to-device copy once the read has finished
+        self._read_pool: List[torch.Tensor] = []
+        self._read_free: List[int] = []
+        self._read_pending: Dict[int, Tuple[int, int]] = {}          # block id -> (ticket, pool index)
+        self._read_copying: List[Tuple[int, "torch.cuda.Event"]] = []  # (pool index, copy-done event)
 
     # ------------------------------------------------------------------------------------------
     def access_sequence(self) -> RingAttentionAccessSequence:
@@ -278,6 +284,9 @@ class BeladyKVCacheTieringManager:
             slots = self.num_layers * self.blocks_per_layer
             self._file = _ext.host().FileTier(self.nvme_path, self.block_bytes, slots, 2, self.block_bytes % 4096 == 0)
             self._bounce = torch.empty(self.block_elems, dtype=self.dtype).pin_memory()
+            self._read_pool = [torch.empty(self.block_elems, dtype=self.dtype).pin_memory()
+                               for _ in range(self.lookahead + 2)]
+            self._read_free = list(range(len(self._read_pool)))
 
     def _hbm_bytes(self) -> int:
         return len(self._hbm) * self.block_bytes
@@ -320,31 +329,64 @@ class BeladyKVCacheTieringManager:
         else:
             raise MemoryError("KV does not fit the HBM and DRAM budgets and no nvme_path was given")
 
-    def _start_load(self, bid: int) -> None:
-        """Begins bringing block `bid` into HBM on the copy stream."""
-        if bid in self._hbm or bid in self._inflight:
-            return
+    def _reclaim_read_buffers(self, block: bool = False) -> None:
+        """Returns pool buffers whose host-to-device copy has finished to the free list."""
+        keep = []
+        for idx, ev in self._read_copying:
+            if block:
+                ev.synchronize()
+            if ev.query():
+                self._read_free.append(idx)
+            else:
+                keep.append((idx, ev))
+        self._read_copying = keep
+
+    def _finish_file_read(self, bid: int) -> None:
+        """Waits for the worker thread's read of `bid`, then starts its copy into HBM."""
+        ticket, idx = self._read_pending.pop(bid)
+        if self._file.wait(ticket) != 0:
+            raise IOError(f"reading KV block {bid} from {self.nvme_path} failed")
+        self._stats.bytes_nvme_read += self.block_bytes
         dev = torch.empty(self.block_elems, dtype=self.dtype, device="cuda")
-        if bid in self._dram:
-            src = self._dram[bid]
-        elif bid in self._on_disk:
-            ticket = self._file.read_async(bid, self._bounce.data_ptr(), self.block_bytes)
-            if self._file.wait(ticket) != 0:
-                raise IOError(f"reading KV block {bid} from {self.nvme_path} failed")
-            self._stats.bytes_nvme_read += self.block_bytes
-            src = self._bounce
-        else:
-            raise KeyError(f"KV block {bid} was never registered")
         with torch.cuda.stream(self._copy_stream):
-            dev.copy_(src, non_blocking=True)
+            dev.copy_(self._read_pool[idx], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
-        if src is self._bounce:
-            ev.synchronize()  # the bounce buffer is reused by the next file read
+        self._read_copying.append((idx, ev))
         self._hbm[bid] = dev
         self._inflight[bid] = ev
         self._stats.bytes_h2d += self.block_bytes
         self._stats.peak_hbm_bytes = max(self._stats.peak_hbm_bytes, self._hbm_bytes())
+
+    def _start_load(self, bid: int, must: bool = False) -> None:
+        """Begins bringing block `bid` into HBM: from pinned DRAM a copy on the copy stream; from the
+        file tier a worker-thread read into a pinned pool buffer (the copy follows when it has
+        landed). `must`: the block is needed now, so wait for a pool buffer instead of giving up."""
+        if bid in self._hbm or bid in self._inflight or bid in self._read_pending:
+            return
+        if bid in self._dram:
+            dev = torch.empty(self.block_elems, dtype=self.dtype, device="cuda")
+            with torch.cuda.stream(self._copy_stream):
+                dev.copy_(self._dram[bid], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+            self._hbm[bid] = dev
+            self._inflight[bid] = ev
+            self._stats.bytes_h2d += self.block_bytes
+            self._stats.peak_hbm_bytes = max(self._stats.peak_hbm_bytes, self._hbm_bytes())
+        elif bid in self._on_disk:
+            self._reclaim_read_buffers()
+            if not self._read_free:
+                if not must:
+                    return                          # every pool buffer is busy: try again at the next access
+                for other in list(self._read_pending):   # finish what is queued, then wait for a copy to drain
+                    self._finish_file_read(other)
+                self._reclaim_read_buffers(block=True)
+            idx = self._read_free.pop()
+            ticket = self._file.read_async(bid, self._read_pool[idx].data_ptr(), self.block_bytes)
+            self._read_pending[bid] = (ticket, idx)
+        else:
+            raise KeyError(f"KV block {bid} was never registered")
 
     def step_begin(self) -> None:
         self._cursor = 0
@@ -367,7 +409,7 @@ class BeladyKVCacheTieringManager:
             self._stats.hits += 1
         else:
             self._stats.misses += 1
-            if bid not in self._hbm:
+            if bid not in self._hbm and bid not in self._read_pending:
                 while self._hbm_bytes() + self.block_bytes > self.hbm_budget_bytes and self._hbm:
                     # out-of-plan request: drop the resident block whose next planned use is farthest
                     far = max((b for b in self._hbm if b not in self._inflight),
@@ -375,7 +417,11 @@ class BeladyKVCacheTieringManager:
                     if far is None:
                         break
                     self._hbm.pop(far)
-                self._start_load(bid)
+                self._start_load(bid, must=True)
+            if bid in self._read_pending:              # the file read was started (now or by a prefetch): land it
+                t0 = time.perf_counter()
+                self._finish_file_read(bid)
+                self._stats.exposed_stall_ms += (time.perf_counter() - t0) * 1e3
         ev = self._inflight.pop(bid, None)
         if ev is not None:
             if not ev.query():
@@ -398,12 +444,19 @@ class BeladyKVCacheTieringManager:
 
     def _prefetch_ahead(self) -> None:
         plan = self.plan()
+        # file reads queued at an earlier access have had a whole access to finish: land them, so that their
+        # host-to-device copies run under the next accesses' math
+        if self._read_pending:
+            t0 = time.perf_counter()
+            for bid in list(self._read_pending):
+                self._finish_file_read(bid)
+            self._stats.exposed_stall_ms += (time.perf_counter() - t0) * 1e3
         end = min(len(plan.ids), self._cursor + self.lookahead)
         for j in range(self._cursor, end):
             bid = plan.ids[j]
-            if bid in self._hbm:
+            if bid in self._hbm or bid in self._read_pending:
                 continue
-            if self._hbm_bytes() + self.block_bytes > self.hbm_budget_bytes:
+            if self._hbm_bytes() + (len(self._read_pending) + 1) * self.block_bytes > self.hbm_budget_bytes:
                 break
             self._start_load(bid)
 
@@ -411,8 +464,13 @@ class BeladyKVCacheTieringManager:
         """Blocks stay resident until the plan evicts them; nothing to do."""
 
     def step_end(self) -> None:
+        for bid in list(self._read_pending):        # reads nobody asked for in the end: let them finish, drop them
+            ticket, idx = self._read_pending.pop(bid)
+            self._file.wait(ticket)
+            self._read_free.append(idx)
         if self._copy_stream is not None:
             self._copy_stream.synchronize()
+        self._reclaim_read_buffers(block=True)
         self._inflight.clear()
 
     def stats(self) -> TierStats:
