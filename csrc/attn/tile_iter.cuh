@@ -9,10 +9,18 @@
 // With a 4096-token window over 262,144 tokens a plain scan visits 2,048 tiles to find ~64.
 #pragma once
 
+// The functions are plain index arithmetic: compiled for the device by nvcc and, for the host-side
+// exhaustive check against a brute-force scan (csrc/attn/tile_iter_host.cpp), by the host compiler.
+#if defined(__CUDACC__)
+#define ZX_TI_FN __host__ __device__ __forceinline__
+#else
+#define ZX_TI_FN inline
+#endif
+
 namespace zx {
 
 template <class P>
-__device__ __forceinline__ bool ti_allowed(const P& p, int qpos0, int kpos0) {
+ZX_TI_FN bool ti_allowed(const P& p, int qpos0, int kpos0) {
   if (p.causal && kpos0 > qpos0) return false;
   if (p.window_blocks > 0) {
     const int qb = qpos0 >> 7, kb = kpos0 >> 7;
@@ -26,7 +34,7 @@ __device__ __forceinline__ bool ti_allowed(const P& p, int qpos0, int kpos0) {
 
 // Smallest KV tile j' >= j that Q tile position qpos0 may attend; n_kv_tiles if none.
 template <class P>
-__device__ __forceinline__ int next_kv_tile(const P& p, int qpos0, int j) {
+ZX_TI_FN int next_kv_tile(const P& p, int qpos0, int j) {
   const int n = p.n_kv_tiles, per = p.kv_tiles_per_chunk;
   const int qb = qpos0 >> 7;
   while (j < n) {
@@ -58,14 +66,14 @@ struct KvCursor {
   int c, base_j, end_j, chunk_pos;
 
   template <class P>
-  __device__ __forceinline__ void init(const P& p, int qpos0) {
+  ZX_TI_FN void init(const P& p, int qpos0) {
     c = 0; base_j = 0; end_j = p.kv_tiles_per_chunk < p.n_kv_tiles ? p.kv_tiles_per_chunk : p.n_kv_tiles;
     chunk_pos = p.kv_chunk_pos[0];
     seek(p, qpos0, 0);
   }
   // moves to the first allowed tile at or after `from` (from >= the current tile)
   template <class P>
-  __device__ __forceinline__ void seek(const P& p, int qpos0, int from) {
+  ZX_TI_FN void seek(const P& p, int qpos0, int from) {
     const int n = p.n_kv_tiles, qb = qpos0 >> 7;
     int jj = from;
     while (true) {
@@ -98,13 +106,13 @@ struct PairWalk {
   bool need0, need1;
   KvCursor cur[2];
   template <class P>
-  __device__ __forceinline__ void init(const P& p, int qpos_a, int qpos_b, bool has_b) {
+  ZX_TI_FN void init(const P& p, int qpos_a, int qpos_b, bool has_b) {
     j = -1; need0 = need1 = false;
     cur[0].init(p, qpos_a);
     if (has_b) cur[1].init(p, qpos_b); else cur[1].j = p.n_kv_tiles;
   }
   template <class P>
-  __device__ __forceinline__ bool advance(const P& p, int qpos_a, int qpos_b, bool has_b) {
+  ZX_TI_FN bool advance(const P& p, int qpos_a, int qpos_b, bool has_b) {
     j = cur[0].j < cur[1].j ? cur[0].j : cur[1].j;
     if (j >= p.n_kv_tiles) return false;
     need0 = cur[0].j == j;
@@ -117,7 +125,7 @@ struct PairWalk {
 
 // Smallest Q tile t' >= t that may attend KV tile position kpos0; n_q_tiles if none.
 template <class P>
-__device__ __forceinline__ int next_q_tile(const P& p, int kpos0, int t) {
+ZX_TI_FN int next_q_tile(const P& p, int kpos0, int t) {
   const int n = p.n_q_tiles, per = p.q_tiles_per_chunk;
   const int kb = kpos0 >> 7;
   const bool kv_global = p.window_blocks > 0 && p.global_every > 0 && (kb % p.global_every) == 0;

@@ -5,6 +5,7 @@
 #include <pybind11/stl.h>
 
 #include "cpu_ref/flash_cpu.h"
+#include "attn/tile_iter_host.h"
 #include "peer/barrier_model.h"
 #include "tier/belady_min.h"
 #include "tier/tier_engine.h"
@@ -44,6 +45,9 @@ CpuAttnShape shape_of(const FArr& q, const FArr& k, float scale, bool causal, in
 }  // namespace
 
 PYBIND11_MODULE(_host, m) {
+  m.def("tile_iter_mismatches", &zx::tile_iter_mismatches, py::arg("causal"), py::arg("window_blocks"),
+        py::arg("global_every"), py::arg("q_chunk_pos"), py::arg("kv_chunk_pos"), py::arg("q_tiles_per_chunk"),
+        py::arg("kv_tiles_per_chunk"));
   m.def("barrier_model", [](int ranks, int rounds, uint32_t start_epoch, uint64_t seed, int absent_rank,
                             int absent_from_round, int64_t timeout_us) {
     zx::BarrierModelResult r;

@@ -146,3 +146,30 @@ def test_peer_barrier_protocol_model_under_random_interleavings():
     assert r["violations"] == 0 and r["timeouts"] == 0 and r["rounds_done"] == 80, r
     r = h.barrier_model(3, 40, 0, 9, absent_rank=1, absent_from_round=10, timeout_us=20000)
     assert r["violations"] == 0 and r["timeouts"] >= 1 and r["rounds_done"] == 10, r
+
+
+def test_attention_tile_iteration_equals_a_plain_scan():
+    """The mask-aware tile iteration of the attention kernels (jumps over excluded runs, division-free
+    cursors, the forward kernel's pair walk), compiled for the host, against a brute-force scan with the
+    same mask predicate: dense, causal, one- and two-sided windows, global blocks, and position layouts
+    in one, two (zigzag) and many out-of-order chunks, for every Q tile and every KV tile."""
+    import random
+
+    from zenyx_b200.ops import _ext
+
+    h = _ext.host()
+    rng = random.Random(0)
+    cases = [(False, 0, 0, [0], [0], 8, 8), (True, 0, 0, [0], [0], 16, 16),
+             (True, 32, 64, [0], [0], 256, 256),                              # 32K tokens, 4096 window, global every 64
+             (True, 2, 4, [0, 3 * 1024], [0, 3 * 1024], 8, 8),                # zigzag rank 0 of a ring of 2
+             (True, 3, 0, [1024, 2048], [0, 3 * 1024], 8, 8)]                 # Q of rank 1 against KV of rank 0
+    for _ in range(60):
+        nq, nk = rng.choice([1, 2, 4, 8]), rng.choice([1, 2, 4, 8])
+        per_q, per_k = rng.choice([1, 2, 3, 8]), rng.choice([1, 2, 5, 8])
+        span = 64
+        qc = [128 * per_q * c for c in rng.sample(range(span), nq)]
+        kc = [128 * per_k * c for c in rng.sample(range(span), nk)]
+        cases.append((rng.random() < 0.6, rng.choice([0, 1, 2, 5, 9]), rng.choice([0, 1, 3, 4, 16]), qc, kc, per_q, per_k))
+    for causal, wb, ge, qc, kc, per_q, per_k in cases:
+        bad = h.tile_iter_mismatches(causal, wb, ge, qc, kc, per_q, per_k)
+        assert bad == 0, (causal, wb, ge, qc, kc, per_q, per_k, bad)

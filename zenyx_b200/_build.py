@@ -36,7 +36,7 @@ CUDA_SOURCES = [
     "noalloc/attn_bwd_static.cu",
 ]
 CUDA_CPP_SOURCES = ["bindings.cpp", "peer/ipc_memory.cpp"]
-HOST_SOURCES = ["tier/belady_min.cpp", "tier/tier_engine.cpp", "cpu_ref/flash_cpu.cpp", "peer/barrier_model.cpp",
+HOST_SOURCES = ["tier/belady_min.cpp", "tier/tier_engine.cpp", "cpu_ref/flash_cpu.cpp", "peer/barrier_model.cpp", "attn/tile_iter_host.cpp",
                 "host_bindings.cpp"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
