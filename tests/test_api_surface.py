@@ -100,3 +100,24 @@ def test_loader_roundtrip_and_validate_module(tmp_path):
     loader.load_into(dst2, f2)
     assert torch.equal(dst2[1].weight, src[1].weight)
     assert len(validate.CHECKS) >= 6 and "plan" in validate._belady() or True
+
+
+def test_examples_run_on_cpu(tmp_path):
+    """examples/01 (any nn.Module through the Trainer) trains, and examples/03 prints the plans and runs the
+    sparse and FP8-KV attention modules on the device that is present."""
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def load(name):
+        spec = importlib.util.spec_from_file_location(name.replace(".py", ""), os.path.join(root, "examples", name))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    hist = load("01_quickstart_any_module.py").main(epochs=2, out=str(tmp_path / "m.json"))
+    assert hist[1] < hist[0] and (tmp_path / "m.json").exists()
+    ex3 = load("03_long_context_four_pillars.py")
+    ex3.describe()
+    ex3.small_run()
