@@ -356,7 +356,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_fmt, int b
 
 // ----------------------------------------------------------------------------------------------
 // Fused peer pull: one warp copies this CTA's slice of a (possibly remote) buffer into local
-// memory with 16-byte loads, four in flight per lane. Sizes are in 16-byte vectors.
+// memory with 16-byte loads, several in flight per lane. Sizes are in 16-byte vectors.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
   uint4 v;
@@ -366,6 +366,10 @@ __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
                : "memory");
   return v;
 }
+// DEPTH 16-byte loads are in flight per lane: a peer load takes about 2 us over NVLink, so the copy rate of
+// one warp is DEPTH * 32 * 16 B per round trip, and 148 such warps need DEPTH >= 8 to keep up with a GEMM or
+// attention launch of a few hundred microseconds.
+template <int DEPTH = 8>
 __device__ __forceinline__ void warp_pull_slice(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t nvec,
                                                 int lane) {
   if (src == nullptr || nvec == 0) return;
@@ -374,13 +378,12 @@ __device__ __forceinline__ void warp_pull_slice(const uint4* __restrict__ src, u
   size_t end = begin + per;
   if (end > nvec) end = nvec;
   size_t i = begin + lane;
-  for (; i + 96 < end; i += 128) {
-    const uint4 a = ld_stream_v4(src + i), b = ld_stream_v4(src + i + 32), c = ld_stream_v4(src + i + 64),
-                d = ld_stream_v4(src + i + 96);
-    dst[i] = a;
-    dst[i + 32] = b;
-    dst[i + 64] = c;
-    dst[i + 96] = d;
+  for (; i + 32 * (DEPTH - 1) < end; i += 32 * DEPTH) {
+    uint4 v[DEPTH];
+#pragma unroll
+    for (int k = 0; k < DEPTH; ++k) v[k] = ld_stream_v4(src + i + 32 * k);
+#pragma unroll
+    for (int k = 0; k < DEPTH; ++k) dst[i + 32 * k] = v[k];
   }
   for (; i < end; i += 32) dst[i] = ld_stream_v4(src + i);
 }

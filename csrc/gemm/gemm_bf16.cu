@@ -186,7 +186,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == W_PULL) {
     // ------------------------------- peer pull ----------------------------------
-    warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
+    warp_pull_slice<16>(p.pull_src, p.pull_dst, p.pull_nvec, lane);
   } else {
     // ------------------------------- epilogue warps -----------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read

@@ -149,7 +149,7 @@ def case_tp(ctx):
         gen = torch.Generator().manual_seed(100 + trial)
         x_all = torch.randn(R * m, K, generator=gen)
         w = (torch.randn(N, K, generator=gen) / math.sqrt(K))
-        y = allgather_gemm(x_all[r * m: (r + 1) * m].cuda().bfloat16(), w.cuda().bfloat16(), fc)
+        y = allgather_gemm(x_all[r * m: (r + 1) * m].cuda().bfloat16(), w.cuda().bfloat16(), fc, fused=True)
         _ext.check_status()
         ref = x_all.bfloat16().float() @ w.bfloat16().float().t()
         assert rel(y.cpu(), ref) < 1e-2, ("allgather_gemm", trial, rel(y.cpu(), ref))
@@ -157,9 +157,13 @@ def case_tp(ctx):
         Kl = K // R
         xr = x_all[:, r * Kl: (r + 1) * Kl].cuda().bfloat16()
         wr = w[:, r * Kl: (r + 1) * Kl].cuda().bfloat16()
-        yr = gemm_reduce_scatter(xr, wr, fc)
+        yr = gemm_reduce_scatter(xr, wr, fc, fused=True)
         _ext.check_status()
         assert rel(yr.cpu(), ref[r * m: (r + 1) * m]) < 1e-2, ("gemm_reduce_scatter", trial, rel(yr.cpu(), ref[r * m: (r + 1) * m]))
+        # the automatic choice (fused or library collective, by size and rank count) gives the same numbers
+        ya = allgather_gemm(x_all[r * m: (r + 1) * m].cuda().bfloat16(), w.cuda().bfloat16(), fc)
+        yra = gemm_reduce_scatter(xr, wr, fc)
+        assert rel(ya.cpu(), ref) < 1e-2 and rel(yra.cpu(), ref[r * m: (r + 1) * m]) < 1e-2
     fc.close()
     print(f"rank {r}: tp ok", flush=True)
 

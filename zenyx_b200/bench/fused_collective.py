@@ -74,9 +74,9 @@ def main(argv=None):
 
     rows = []
     for name, fused, unfused, flops, wire in (
-        ("allgather_gemm", lambda: allgather_gemm(x_local, w_col, fc), unfused_ag,
+        ("allgather_gemm", lambda: allgather_gemm(x_local, w_col, fc, fused=True), unfused_ag,
          2.0 * T * D * n_col, (R - 1) * m * D * 2),
-        ("gemm_reduce_scatter", lambda: gemm_reduce_scatter(a_full, w_row, fc), unfused_rs,
+        ("gemm_reduce_scatter", lambda: gemm_reduce_scatter(a_full, w_row, fc, fused=True), unfused_rs,
          2.0 * T * k_row * D, (R - 1) * m * D * 4),
     ):
         ms_f = _time(fused)

@@ -68,13 +68,27 @@ class FusedCollectiveContext:
         self.slots.close()
 
 
+# One pull warp per CTA keeps 16 loads of 16 bytes in flight per lane and a peer load takes about 2 us, so
+# the 148 warps of a launch copy about 600 GB/s; the NVLink port itself gives 770 GB/s.
+_PULL_BYTES_PER_S = 6.0e11
+_GEMM_FLOPS_PER_S = 1.3e15
+
+
+def _pull_hides_under_gemm(m: int, k: int, n: int) -> bool:
+    """Whether copying one [m, k] bf16 shard fits underneath one [m, k] x [n, k]^T launch."""
+    return 2.0 * m * k * n / _GEMM_FLOPS_PER_S >= 2.0 * m * k / _PULL_BYTES_PER_S
+
+
 def allgather_gemm(x_local: torch.Tensor, w: torch.Tensor, ctx: Optional[FusedCollectiveContext] = None,
-                   group=None, trans_b: bool = False, gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   group=None, trans_b: bool = False, gathered: Optional[torch.Tensor] = None,
+                   fused: Optional[bool] = None) -> torch.Tensor:
     """``concat over ranks of x_local`` times ``w^T`` (``w`` itself when ``trans_b``: w stored [K, N]).
 
     Returns [world * m, N] on every rank. ``gathered`` ([world * m, K]), when given, receives the
     gathered operand: the pull warps then copy each remote shard straight into its rows and the
     GEMMs read it from there, so the caller keeps it (for a weight gradient) at no extra traffic.
+    ``fused``: None picks the fused path when one shard's copy fits under one launch's math (it does for
+    n >= ~1100 output features per rank) and the NCCL all-gather + one GEMM otherwise.
     """
     world, rank = _world(group), _rank(group)
     m, k = x_local.shape
@@ -82,7 +96,10 @@ def allgather_gemm(x_local: torch.Tensor, w: torch.Tensor, ctx: Optional[FusedCo
         if gathered is not None:
             gathered.copy_(x_local)
         return gemm(x_local, w, trans_b=trans_b)
-    if not (_ext.use_cuda_kernels(x_local) and ctx is not None):
+    n_feat = w.shape[1] if trans_b else w.shape[0]
+    if fused is None:
+        fused = _pull_hides_under_gemm(m, k, n_feat)
+    if not (_ext.use_cuda_kernels(x_local) and ctx is not None and fused):
         parts = [torch.empty_like(x_local) for _ in range(world)]
         dist.all_gather(parts, x_local.contiguous(), group=group)
         full = torch.cat(parts, dim=0)
@@ -121,19 +138,32 @@ def allgather_gemm(x_local: torch.Tensor, w: torch.Tensor, ctx: Optional[FusedCo
 
 
 def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, ctx: Optional[FusedCollectiveContext] = None,
-                        group=None, trans_b: bool = False) -> torch.Tensor:
+                        group=None, trans_b: bool = False, fused: Optional[bool] = None) -> torch.Tensor:
     """Rows ``[rank * m, (rank + 1) * m)`` of ``sum over ranks of x @ w^T`` (x: [world * m, K_local];
-    ``w`` is [N, K_local], or [K_local, N] with ``trans_b``)."""
+    ``w`` is [N, K_local], or [K_local, N] with ``trans_b``).
+
+    ``fused``: None uses the scatter epilogue on 2 ranks (measured 1.05x over GEMM + NCCL) and GEMM + NCCL
+    reduce-scatter beyond: the epilogue writes each thread's row in 16-byte pieces, which the local L2
+    merges but NVLink carries one by one, and with 7/8 of the rows remote it measured 0.17x on 8 GPUs.
+    A shared-memory-staged epilogue writing whole 128-byte row segments is what the fused path needs there.
+    """
     world, rank = _world(group), _rank(group)
     M = x.shape[0]
     if world == 1:
         return gemm(x, w, trans_b=trans_b)
     assert M % world == 0, "rows must split evenly over the group"
     m, n = M // world, (w.shape[1] if trans_b else w.shape[0])
-    if not (_ext.use_cuda_kernels(x) and ctx is not None):
+    if fused is None:
+        fused = world == 2
+    if not _ext.use_cuda_kernels(x):
         y = gemm(x, w, trans_b=trans_b, out_dtype=torch.float32)
         dist.all_reduce(y, group=group)             # gloo has no reduce_scatter
         return y[rank * m: (rank + 1) * m].to(x.dtype)
+    if ctx is None or not fused:
+        y = gemm(x, w, trans_b=trans_b)
+        out = torch.empty(m, n, device=x.device, dtype=x.dtype)
+        dist.reduce_scatter_tensor(out, y, group=group)
+        return out
     assert m <= ctx.rows and n <= ctx.n and x.dtype == torch.bfloat16
     C = _ext.C()
     slots = ctx.slots_view(m, n)                    # [world, m, n]; slot q receives rank q's partial of my rows
