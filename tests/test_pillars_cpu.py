@@ -235,3 +235,13 @@ def test_split_master_is_exact():
     hi, lo = fused.split_master(w)
     assert torch.equal(fused.join_master(hi, lo), w)
     assert ((hi.float() - w).abs() <= w.abs() * 2 ** -8 + 1e-38).all()
+
+
+def test_fused_collective_path_choice_follows_the_measurements():
+    """allgather_gemm fuses when one shard's copy fits under one launch's math; the 8-GPU and 2-GPU shapes that
+    were measured land on the side the measurements say."""
+    from zenyx_b200.parallel.fused_collective import _pull_hides_under_gemm
+
+    assert _pull_hides_under_gemm(16384, 4096, 14336)        # 2 GPUs, gate|up: fused measured 1.19x
+    assert _pull_hides_under_gemm(4096, 4096, 3584)          # 8 GPUs with the 16-deep pull: 56 us copy, 92 us math
+    assert not _pull_hides_under_gemm(4096, 4096, 512)       # a narrow projection cannot hide its operand's copy
