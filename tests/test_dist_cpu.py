@@ -335,3 +335,44 @@ def _failure_detection(rank, world):
 
 def test_heartbeat_detects_a_stalled_rank_on_the_host():
     run_ranks(_failure_detection)
+
+
+# ------------------------------------------------------------------------------------------------
+def _elastic(rank, world, tmp):
+    """Three data-parallel gloo ranks train a tiny Llama; rank 2 leaves between steps (host-side exit, nothing in
+    flight); the other two notice, agree on the roster, form a 2-rank group, resume from the last checkpoint
+    (sharded optimizer state re-sharded 3 -> 2) and finish the run."""
+    from zenyx_b200.models import LlamaConfig
+    from zenyx_b200.train import Trainer, TrainerConfig, loop
+    from zenyx_b200.train import checkpoint as ckpt
+    from zenyx_b200.train.elastic import ElasticConfig, run_elastic
+
+    cfg = LlamaConfig.tiny(n_layers=1, d_model=64, n_heads=2, n_kv_heads=1, ffn_dim=96, vocab_size=128)
+    seq, batch, steps = 128, 6, 6
+
+    def make_trainer():
+        return Trainer(cfg, TrainerConfig(lr=5e-3, seq_len=seq, global_batch=batch, ring_degree=1, max_grad_norm=1.0, seed=1))
+
+    def make_data(r, w):
+        gen = torch.Generator().manual_seed(7)
+        while True:
+            x = torch.randint(0, 128, (batch, seq), generator=gen)
+            yield x, torch.roll(x, -1, dims=1)
+
+    def fault(step):
+        if rank == 2 and step == 3:
+            os._exit(0)          # leaves between steps, the way a crashed host process would
+
+    records, coord = run_elastic(make_trainer, make_data,
+                                 loop.LoopConfig(steps=steps, log_every=0, checkpoint_every=2,
+                                                 checkpoint_dir=os.path.join(tmp, "ckpt"), resume=True),
+                                 ElasticConfig(rendezvous_dir=os.path.join(tmp, "rdzv"), heartbeat_timeout_s=2.0,
+                                               settle_s=1.0, group_timeout_s=60.0), before_step=fault)
+    assert coord.generation == 1 and dist.get_world_size() == 2 and dist.get_rank() == rank
+    assert records[0]["step"] == 2 and records[-1]["step"] == steps - 1      # resumed from the step-2 checkpoint
+    assert all(math.isfinite(r["loss"]) for r in records)
+    assert ckpt.latest_step(os.path.join(tmp, "ckpt")) == steps
+
+
+def test_elastic_regroup_after_a_rank_leaves(tmp_path):
+    run_ranks(_elastic, world=3, args=(str(tmp_path),))
