@@ -173,3 +173,41 @@ def test_attention_tile_iteration_equals_a_plain_scan():
     for causal, wb, ge, qc, kc, per_q, per_k in cases:
         bad = h.tile_iter_mismatches(causal, wb, ge, qc, kc, per_q, per_k)
         assert bad == 0, (causal, wb, ge, qc, kc, per_q, per_k, bad)
+
+
+def test_tracing_helpers_and_loop_metrics(tmp_path):
+    """PhaseTimer accumulates per-phase time, trace ranges are no-ops without a GPU, and the training loop's
+    JSON-lines records carry tokens/s, MFU, ring and data-parallel degree for the flagship."""
+    import json
+
+    from zenyx_b200.models import LlamaConfig
+    from zenyx_b200.train import Trainer, TrainerConfig, loop
+    from zenyx_b200.utils import tracing
+
+    t = tracing.PhaseTimer()
+    with t.phase("a"):
+        with tracing.trace_range("inner"):
+            sum(range(1000))
+    with t.phase("a"):
+        pass
+    assert set(t.summary()) == {"a"} and t.summary()["a"] >= 0.0
+    tracing.enable(True)
+    assert tracing.enabled()
+    with tracing.trace_range("x"):
+        pass
+    tracing.enable(False)
+    cfg = LlamaConfig.tiny(n_layers=1, d_model=64, n_heads=2, n_kv_heads=1, ffn_dim=96, vocab_size=128)
+    tr = Trainer(cfg, TrainerConfig(lr=1e-3, seq_len=128, global_batch=2))
+
+    def data():
+        g = torch.Generator().manual_seed(0)
+        while True:
+            x = torch.randint(0, 128, (2, 128), generator=g)
+            yield x, x
+
+    path = str(tmp_path / "metrics.jsonl")
+    loop.run(tr, data(), cfg=loop.LoopConfig(steps=2, log_every=0, metrics_path=path, tokens_per_step=256))
+    tr.close()
+    recs = [json.loads(l) for l in open(path)]
+    assert len(recs) == 2 and all(k in recs[0] for k in ("step", "loss", "tokens_per_s", "mfu", "ring_degree", "dp_degree"))
+    assert recs[0]["mfu"] > 0

@@ -32,6 +32,7 @@ import torch.nn as nn
 from ..ops import fused
 from ..ops.attention import RingContext, ring_attn_backward, ring_attn_forward
 from ..ops.gemm import gemm
+from ..utils.tracing import trace_range
 
 
 @dataclass
@@ -440,18 +441,23 @@ class LlamaModel(nn.Module):
         if loss_weight is None:
             loss_weight = 1.0 / (B * S * ring.degree)
         with torch.no_grad():
-            h = fused.embedding_fwd(tokens, self.w("embed.weight"))
+            with trace_range("embedding"):
+                h = fused.embedding_fwd(tokens, self.w("embed.weight"))
             saved_all = []
             for l in range(self.cfg.n_layers):
-                h, saved = self._layer_forward(l, h, B, S, ring, keep=True)
+                with trace_range(f"layer{l}.forward"):
+                    h, saved = self._layer_forward(l, h, B, S, ring, keep=True)
                 saved_all.append(saved)
             if "gu@host" in self.remat.saved and h.is_cuda:
                 self._start_fetch_gu(self.cfg.n_layers - 1)   # under the LM head instead of in front of the last layer
-            loss, dh = self._head_loss(h, targets, loss_weight, want_grad=True)
+            with trace_range("head+loss"):
+                loss, dh = self._head_loss(h, targets, loss_weight, want_grad=True)
             del h
             for l in reversed(range(self.cfg.n_layers)):
-                dh = self._layer_backward(l, dh, saved_all.pop(), B, S, ring)
-            fused.embedding_bwd(tokens, dh, self.g("embed.weight"))
+                with trace_range(f"layer{l}.backward"):
+                    dh = self._layer_backward(l, dh, saved_all.pop(), B, S, ring)
+            with trace_range("embedding.backward"):
+                fused.embedding_bwd(tokens, dh, self.g("embed.weight"))
         return loss
 
     def forward(self, tokens: torch.Tensor, ring: Optional[RingContext] = None) -> torch.Tensor:

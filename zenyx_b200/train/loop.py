@@ -64,6 +64,12 @@ def run(trainer: Trainer, data_iter: Iterable, criterion=None, cfg: Optional[Loo
             rec: Dict[str, Any] = {"step": step, "loss": loss, "step_s": dt}
             if cfg.tokens_per_step:
                 rec["tokens_per_s"] = cfg.tokens_per_step / dt
+                mcfg = getattr(trainer.model, "cfg", None)
+                if trainer.engine is not None and mcfg is not None and hasattr(mcfg, "flops_per_token"):
+                    from ..planner import HardwarePeaks   # model FLOPs utilisation against the measured sustained GEMM rate
+
+                    peak = HardwarePeaks.load().bf16_tflops * 1e12 * trainer.ctx.world_size
+                    rec["mfu"] = mcfg.flops_per_token(trainer.config.seq_len) * rec["tokens_per_s"] / peak
             if trainer.engine is not None:
                 rec["ring_degree"] = trainer.engine.ring_degree
                 rec["dp_degree"] = trainer.ctx.world_size // trainer.engine.ring_degree
