@@ -121,3 +121,30 @@ def test_examples_run_on_cpu(tmp_path):
     ex3 = load("03_long_context_four_pillars.py")
     ex3.describe()
     ex3.small_run()
+
+
+def test_added_modules_import_and_export_their_entry_points():
+    """Everything this package adds beside the reference's surface is importable on a machine without a GPU."""
+    import importlib
+
+    expected = {
+        "zenyx_b200.loader": ["load_into", "load_safetensors", "save_checkpoint", "load_checkpoint"],
+        "zenyx_b200.ops.comm": ["ring_exchange", "ring_all_gather", "ring_reduce_scatter"],
+        "zenyx_b200.ops.vocab": ["vocab_parallel_cross_entropy"],
+        "zenyx_b200.parallel.fused_collective": ["allgather_gemm", "gemm_reduce_scatter", "FusedCollectiveContext",
+                                                 "allgather_linear", "linear_reduce_scatter"],
+        "zenyx_b200.train.elastic": ["ElasticConfig", "ElasticCoordinator", "run_elastic"],
+        "zenyx_b200.utils.tracing": ["trace_range", "PhaseTimer", "enable"],
+        "zenyx_b200.validate": ["main", "CHECKS"],
+        "zenyx_b200.bench.micro": ["build", "NAMES"],
+        "zenyx_b200.bench.kv_tiering": ["main"],
+        "zenyx_b200.bench.fused_collective": ["main"],
+        "zenyx_b200.bench.attn_vs_sdpa": ["main"],
+        "zenyx_b200.bench.step_breakdown": ["main"],
+        "zenyx_b200.bench.cpu_plumbing": ["main"],
+        "zenyx_b200.bench.fp8_kv_error": ["main"],
+    }
+    for mod, names in expected.items():
+        m = importlib.import_module(mod)
+        for n in names:
+            assert hasattr(m, n), (mod, n)
