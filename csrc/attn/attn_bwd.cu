@@ -132,7 +132,6 @@ constexpr int Q_STAGES = 3, DO_STAGES = 2;
 // around it (TMEM round trips, barrier latency, the dS arithmetic) is per-warp serial time, and
 // four warps per scheduler overlap it where two could not.
 constexpr int KW_COMPUTE = 16, KW_TMA = 16, KW_MMA = 17, KW_PULL = 18;
-constexpr int KN_COMPUTE = KW_COMPUTE * 32;
 constexpr int DKDV_THREADS = (KW_COMPUTE + 3) * 32;
 // Tail of the dK/dV kernel's shared memory: alignment slack, barriers, and two buffers of 256
 // per-query statistics (-lse * log2e for 128 queries, then -delta for the same 128).
