@@ -201,8 +201,9 @@ def _ring_helpers_and_vocab_ce(rank, world):
     assert torch.allclose(local.grad, logits.grad[:, rank * vl:(rank + 1) * vl], atol=1e-5)
 
 
-def test_ring_helpers_and_vocab_parallel_cross_entropy():
-    run_ranks(_ring_helpers_and_vocab_ce)
+@pytest.mark.parametrize("world", [2, 3, 4])
+def test_ring_helpers_and_vocab_parallel_cross_entropy(world):
+    run_ranks(_ring_helpers_and_vocab_ce, world=world)
 
 
 # ------------------------------------------------------------------------------------------------
