@@ -57,8 +57,9 @@ def _ring_attention(rank, world):
         assert torch.allclose(dv, sh(dv_ref), atol=1e-4)
 
 
-def test_ring_attention_schedule_matches_full_attention():
-    run_ranks(_ring_attention)
+@pytest.mark.parametrize("world", [2, 3, 4])
+def test_ring_attention_schedule_matches_full_attention(world):
+    run_ranks(_ring_attention, world=world)
 
 
 # ------------------------------------------------------------------------------------------------
