@@ -3,10 +3,11 @@
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
     python bench.py --impl reference ...                     (the reference project's own stack)
 
-Prints ONE JSON line (rank 0). ``value`` is whole-job tokens/s from K optimizer steps timed on the
-device with CUDA events (inputs already resident), max over ranks. ``e2e`` repeats the measurement
-through ``zenyx_b200.train.Trainer.train_step`` with each step's tokens copied from pinned host
-memory and the step's loss read back to the host inside the timed region.
+Prints ONE JSON line (rank 0). The run is ``warmup + steps`` optimizer steps, all of them through the
+public ``zenyx_b200.train.Trainer.train_step``: every step copies its tokens from pinned host memory
+and reads its loss back to the host. The K timed steps are bracketed once, by CUDA events (``value``,
+device time, max over ranks) and by the host clock around the same loop including the final
+synchronisation (``e2e``).
 Synthetic uniform tokens, random-init weights. The model, sequence length and batch are those of
 the baseline configuration; smaller shapes are only reachable through explicit flags and are
 labelled as such in ``config``.
@@ -38,7 +39,8 @@ def parse_args():
     ap.add_argument("--ring-degree", type=int, default=0, help="context-parallel degree (default: the planner chooses dp x cp)")
     ap.add_argument("--no-fused-peer", action="store_true", help="NCCL reduce-scatter/all-gather optimizer path")
     ap.add_argument("--remat", default="auto", choices=["auto", "full", "selective", "none"])
-    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--ring-probe-steps", type=int, default=0,
+                    help="N > 1: also time this many steps with the ring over all N GPUs (secondary key)")
     return ap.parse_args()
 
 
@@ -94,6 +96,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def workload_config(args, parallelism: str, stack: str) -> dict:
+    """The ``config`` entry of the JSON line; both arms print exactly these keys."""
+    valid_shape = args.layers == 32 and args.seq_len == 32768 and args.global_batch == 8
+    return {"model": "llama3-8b-shape" + ("" if valid_shape else f"-DEBUG-{args.layers}L"), "layers": args.layers,
+            "global_batch": args.global_batch, "seq_len": args.seq_len, "dtype": "bf16", "parallelism": parallelism,
+            "stack": stack, "l2": "inputs larger than L2 (weights 16 GB, activations > 126 MB per kernel)"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -118,13 +128,14 @@ def run_ours(args):
     remat = {"auto": None, "full": RematPolicy.full(), "selective": RematPolicy.selective(),
              "none": RematPolicy.none()}[args.remat]
     tcfg = TrainerConfig(lr=3e-4, seq_len=args.seq_len, global_batch=args.global_batch, ring_degree=cp,
-                         weight_decay=0.1, max_grad_norm=1.0, remat=remat, fused_peer=not args.no_fused_peer)
+                         weight_decay=0.1, max_grad_norm=1.0, remat=remat, fused_peer=not args.no_fused_peer,
+                         ring_degrees=(world,) if (args.ring_probe_steps > 0 and world > 1) else ())
     trainer = Trainer(mc, tcfg)
     eng = trainer.engine
     dev = ctx.device
     memory_fallback = None
     B, S = args.global_batch, args.seq_len
-    n_total = args.warmup + 2 * args.steps
+    n_total = args.warmup + args.steps + args.ring_probe_steps
     gen = torch.Generator().manual_seed(1234)
     host_tokens = [torch.randint(0, mc.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(n_total)]
     host_targets = [torch.randint(0, mc.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(n_total)]
@@ -143,7 +154,7 @@ def run_ours(args):
     # ---- warm-up (untimed) ----
     try:
         for i in range(args.warmup):
-            eng.train_step(host_tokens[i], host_targets[i])
+            trainer.train_step(host_tokens[i], host_targets[i])
     except torch.cuda.OutOfMemoryError:
         # The planner sizes the kept activations from the device's total memory; if this box has less of it free
         # than that (a single GPU is planned to 93 %), fall back once to the policy that recomputes the projections.
@@ -160,76 +171,76 @@ def run_ours(args):
         trainer = Trainer(mc, tcfg)
         eng = trainer.engine
         for i in range(args.warmup):
-            eng.train_step(host_tokens[i], host_targets[i])
+            trainer.train_step(host_tokens[i], host_targets[i])
     _ext.check_status()
 
-    # ---- device-timed region: inputs resident on the GPU, K steps ----
-    dev_in = [(eng.shard_batch(host_tokens[args.warmup + i]), eng.shard_batch(host_targets[args.warmup + i]))
-              for i in range(args.steps)]
+    # ---- timed region: K steps through the public API; pinned-host inputs, loss read back every step ----
     sampler = ClockSampler(torch.cuda.current_device())
+    base = args.warmup
     sync_all()
     sampler.start()
     launches0 = _ext.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     e0.record()
-    for tok, tgt in dev_in:
-        eng.train_step(tok, tgt, presharded=True)
+    last = 0.0
+    for i in range(args.steps):
+        last = trainer.train_step(host_tokens[base + i], host_targets[base + i])   # returns a host float
     e1.record()
     sync_all()
+    wall_ms = (time.perf_counter() - t0) * 1e3
     launches = _ext.launch_count - launches0
     clocks = sampler.stop()
     ms_dev = max_over_ranks(e0.elapsed_time(e1))
+    ms_e2e = max_over_ranks(wall_ms)
     _ext.check_status()
-    del dev_in
-
-    # ---- end-to-end region: public API, H2D of the step's tokens and D2H of its loss every step ----
-    e2e = None
-    if not args.skip_e2e:
-        base = args.warmup + args.steps
-        sync_all()
-        t0 = time.perf_counter()
-        e0.record()
-        last = 0.0
-        for i in range(args.steps):
-            last = trainer.train_step(host_tokens[base + i], host_targets[base + i])  # returns a host float
-        e1.record()
-        sync_all()
-        wall_ms = (time.perf_counter() - t0) * 1e3
-        ms_e2e = max(max_over_ranks(e0.elapsed_time(e1)), max_over_ranks(wall_ms))
-        n_local = len(eng.local_sequences())
-        h2d = 2 * n_local * (S // cp) * 8
-        e2e = {"value": round(B * S * args.steps / (ms_e2e / 1e3), 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": round(float(last), 4)}
+    n_local = len(eng.local_sequences())
+    h2d = 2 * n_local * (S // cp) * 8
+    e2e = {"value": round(B * S * args.steps / (ms_e2e / 1e3), 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": round(float(last), 4)}
 
     tokens_per_s = B * S * args.steps / (ms_dev / 1e3)
-    valid_shape = args.layers == 32 and S == 32768 and B == 8
     out = {
         "metric": "8B-shape 32K-ctx train tokens/s", "value": round(tokens_per_s, 1), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 2),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "zenyx_b200",
-        "config": {"model": "llama3-8b-shape" + ("" if valid_shape else f"-DEBUG-{args.layers}L"), "global_batch": B,
-                   "seq_len": S, "parallelism": f"dp{world // cp}xcp{cp}", "remat": list(eng.model.remat.saved),
-                   "optimizer": "sharded AdamW, fp32 master, grad clip 1.0, " +
-                                ("fused P2P reduce-scatter+update+all-gather" if eng.optimizer.fused_peer else "NCCL"),
-                   "l2": "inputs larger than L2 (weights 16 GB, activations > 126 MB per kernel)",
-                   "mfu_of_measured_sustained": None},
+        "config": workload_config(args, f"dp{world // cp}" + (f"xcp{cp}" if cp > 1 else ""),
+                                  "zenyx_b200 Trainer/LlamaEngine: tcgen05 GEMM + flash-attention kernels, sharded AdamW "
+                                  "with fp32 master and grad clip 1.0, " +
+                                  ("fused P2P reduce-scatter+update+all-gather" if eng.optimizer.fused_peer else "NCCL")),
+        "details": {"remat": list(eng.model.remat.saved), "mfu_of_measured_sustained": None},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
     }
     try:
         from zenyx_b200.planner import HardwarePeaks
 
         pk = HardwarePeaks.load()
-        out["config"]["mfu_of_measured_sustained"] = round(
+        out["details"]["mfu_of_measured_sustained"] = round(
             mc.flops_per_token(S) * tokens_per_s / world / (pk.bf16_tflops * 1e12), 4)
-        out["config"]["peaks"] = pk.source
+        out["details"]["peaks"] = pk.source
     except Exception:  # noqa: BLE001
         pass
+    if args.ring_probe_steps > 0 and world > 1 and cp != world:
+        # secondary figure: the same step with the context-parallel ring over all GPUs (first probe step untimed)
+        eng.set_ring_degree(world)
+        pbase = args.warmup + args.steps
+        trainer.train_step(host_tokens[pbase], host_targets[pbase])
+        sync_all()
+        e0.record()
+        for i in range(1, args.ring_probe_steps):
+            trainer.train_step(host_tokens[pbase + i], host_targets[pbase + i])
+        e1.record()
+        sync_all()
+        if args.ring_probe_steps > 1:
+            ms_ring = max_over_ranks(e0.elapsed_time(e1)) / (args.ring_probe_steps - 1)
+            out["details"][f"ring_degree_{world}_tokens_per_s"] = round(B * S / (ms_ring / 1e3), 1)
+        _ext.check_status()
     free_b, total_b = torch.cuda.mem_get_info()
     if memory_fallback:
-        out["config"]["memory_fallback"] = memory_fallback
-    out["config"]["peak_torch_alloc_gb"] = round(torch.cuda.max_memory_allocated() / 1e9, 1)
-    out["config"]["device_mem_used_gb"] = round((total_b - free_b) / 1e9, 1)   # includes peer buffers and the context
+        out["details"]["memory_fallback"] = memory_fallback
+    out["details"]["peak_torch_alloc_gb"] = round(torch.cuda.max_memory_allocated() / 1e9, 1)
+    out["details"]["device_mem_used_gb"] = round((total_b - free_b) / 1e9, 1)   # includes peer buffers and the context
     if rank == 0:
         print(json.dumps(out), flush=True)
     trainer.close()

@@ -14,6 +14,7 @@
 // warps still turn dP into dS), so exponentials and tensor work overlap with a single softmax
 // warpgroup. All waits are bounded.
 #include "../common/ptx.cuh"
+#include "../common/device_once.h"
 #include "../common/tma_host.h"
 #include "attn.h"
 #include "tile_iter.cuh"
@@ -818,7 +819,8 @@ void launch_attn_bwd(const AttnBwdArgs& a) {
   p.pull_nvec = a.pull_src != nullptr ? a.pull_bytes / 16 : 0;
   p.trace = a.trace;
   p.status = a.status;
-  static bool configured = false;
+  static PerDeviceOnce once;
+  bool& configured = once.current();
   if (!configured) {
     set_smem(attn_bwd_dkdv_kernel, DKDV_SMEM, "attn_bwd_dkdv");
     set_smem(attn_bwd_dq_kernel, DQ_SMEM, "attn_bwd_dq");

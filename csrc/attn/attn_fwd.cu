@@ -14,6 +14,7 @@
 // same kernel serves plain sequences, zigzag context-parallel shards and every ring step; with
 // merge_prev it folds its result into the O/LSE left by the previous ring step.
 #include "../common/ptx.cuh"
+#include "../common/device_once.h"
 #include "../common/tma_host.h"
 #include "attn.h"
 #include "tile_iter.cuh"
@@ -28,9 +29,10 @@ constexpr int BKV = 128;
 constexpr int TILE_BYTES = BQ * HD * 2;   // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk: 128 rows x 128 B
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 352;  // 8 softmax warps + TMA + MMA + peer-pull warp
+constexpr int TMA_WARP = 16, MMA_WARP = 17, PULL_WARP = 18;
+constexpr int NUM_THREADS = 19 * 32;  // 16 softmax warps + TMA + MMA + peer-pull warp
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256 + 2 * 2 * 2 * 128 * 4;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
@@ -73,6 +75,21 @@ __device__ __forceinline__ int kv_tile_pos(const FwdParams& p, int j) {
 __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const bool ok = mbar_wait(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
+}
+
+// Rare path of the softmax warps (a row's running maximum grew by more than the threshold): multiply this
+// thread's 64 output columns by alpha in TMEM. Kept out of line so that its 32 extra live registers cost the
+// hot loop nothing; the call's register saves only happen when the branch is taken.
+__device__ __noinline__ void rescale_o_half(uint32_t o_tmem, float alpha) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t orow[32];
+    tmem_ld_32x32b_x32(o_tmem + c * 32, orow);
+    tmem_wait_ld();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
+    tmem_st_32x32b_x32(o_tmem + c * 32, orow);
+  }
 }
 
 #define ZX_FWD_SPARSE 0
@@ -136,7 +153,8 @@ void launch_attn_fwd(const AttnFwdArgs& a) {
   p.pull_dst = (uint4*)a.pull_dst;
   p.pull_nvec = a.pull_src != nullptr ? a.pull_bytes / 16 : 0;
   p.status = a.status;
-  static bool configured = false;
+  static PerDeviceOnce once;
+  bool& configured = once.current();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e == cudaSuccess)

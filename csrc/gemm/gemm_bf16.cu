@@ -9,6 +9,7 @@
 // Every wait is bounded; on a timeout the kernel records a Status and unwinds through the normal
 // teardown (outstanding copies drained, TMEM freed).
 #include "../common/ptx.cuh"
+#include "../common/device_once.h"
 #include "../common/tma_host.h"
 #include "gemm.h"
 
@@ -286,7 +287,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <bool A_MN, bool B_MN>
 void launch_variant(const GemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& p, int grid) {
-  static bool configured = false;
+  static PerDeviceOnce once;
+  bool& configured = once.current();
   auto kern = gemm_bf16_kernel<A_MN, B_MN>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);

@@ -4,6 +4,7 @@
 #include "attn_bwd_static.h"
 
 #include <cuda_runtime.h>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <exception>
@@ -45,6 +46,17 @@ extern "C" int zx_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
                   rows, (int)ZX_ATTN_BWD_NOALLOC_MAX_ROWS);
     return fail(err, err_len, 2, msg);
   }
+  // Everything that can reject the call is checked before anything of the caller's is written.
+  if (Sq % 128 != 0 || Skv % 128 != 0)
+    return fail(err, err_len, 1, "zx_attn_bwd_noalloc: Sq and Skv must be multiples of 128");
+  if (Hq % Hkv != 0) return fail(err, err_len, 1, "zx_attn_bwd_noalloc: Hq must be a multiple of Hkv");
+  if (q_tok_stride < (long long)Hq * 128 || k_tok_stride < (long long)Hkv * 128 || v_tok_stride < (long long)Hkv * 128 ||
+      q_tok_stride % 8 != 0 || k_tok_stride % 8 != 0 || v_tok_stride % 8 != 0)
+    return fail(err, err_len, 1,
+                "zx_attn_bwd_noalloc: token strides must cover all heads and be multiples of 8 elements (16 bytes)");
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)d_o | (uintptr_t)dq | (uintptr_t)dk |
+       (uintptr_t)dv) % 16 != 0)
+    return fail(err, err_len, 1, "zx_attn_bwd_noalloc: tensor pointers must be 16-byte aligned");
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
@@ -58,6 +70,13 @@ extern "C" int zx_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
       return fail(err, err_len, 3, msg);
     }
     g_delta_ptr[dev] = p;
+  }
+  // An error left behind by an earlier, unrelated call must not be blamed on this launch.
+  const cudaError_t pending = cudaPeekAtLastError();
+  if (pending != cudaSuccess) {
+    std::snprintf(msg, sizeof(msg), "zx_attn_bwd_noalloc: an earlier CUDA error is pending on this thread: %s",
+                  cudaGetErrorString(pending));
+    return fail(err, err_len, 7, msg);
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const size_t kv_bytes = (size_t)B * Skv * Hkv * 128 * sizeof(float);

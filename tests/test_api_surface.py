@@ -136,7 +136,6 @@ def test_added_modules_import_and_export_their_entry_points():
         "zenyx_b200.train.elastic": ["ElasticConfig", "ElasticCoordinator", "run_elastic"],
         "zenyx_b200.utils.tracing": ["trace_range", "PhaseTimer", "enable"],
         "zenyx_b200.validate": ["main", "CHECKS"],
-        "zenyx_b200.bench.micro": ["build", "NAMES"],
         "zenyx_b200.bench.kv_tiering": ["main"],
         "zenyx_b200.bench.fused_collective": ["main"],
         "zenyx_b200.bench.attn_vs_sdpa": ["main"],

@@ -210,7 +210,8 @@ def test_checkpoint_roundtrip_and_resume_is_bit_exact(tmp_path):
         o1.step()
     ckpt.save(str(tmp_path), 2, m1, o1, config={"a": 1}, metrics={"loss": 1.0})
     assert ckpt.latest_step(str(tmp_path)) == 2
-    assert sorted(os.listdir(tmp_path / "step_2")) == ["meta.json", "model.safetensors", "optim_rank0of1.safetensors"]
+    assert sorted(os.listdir(tmp_path / "step_2")) == ["meta.json", "model.safetensors", "optim_rank0of1.safetensors",
+                                                       "rng_rank0of1.json"]
     m1.forward_backward(tok, tok)
     o1.step()
     m2, o2 = make()
@@ -228,6 +229,35 @@ def test_checkpoint_roundtrip_and_resume_is_bit_exact(tmp_path):
     m3 = LlamaModel(cfg, seed=99)
     missing, unexpected = load_state_dict_chunked(m3, load_file(str(tmp_path / "step_2" / "model.safetensors")))
     assert not missing and not unexpected
+
+
+def test_flat_layout_does_not_depend_on_world_size_and_state_reshards():
+    """The flat buffer length is the same for every world size, so optimizer shards saved by W ranks
+    stitch to exactly the vector any other rank count slices; vectors from an older layout with a
+    different amount of tail padding are zero-filled or cut."""
+    from zenyx_b200.models.llama import FlatBuffers
+    from zenyx_b200.parallel.zero import ZeroAdamW
+
+    specs = [("a", (37, 129), True), ("b", (1000, 3), True), ("n", (77,), False)]
+    totals = {w: FlatBuffers(specs, "cpu", world_size=w).total for w in (1, 2, 3, 4, 5, 6, 7, 8, 16)}
+    assert len(set(totals.values())) == 1
+    total = totals[1]
+    for w in (2, 3, 4, 8):
+        assert total % (4 * w) == 0
+    flat = FlatBuffers(specs, "cpu")
+    opt = ZeroAdamW(flat, lr=1e-3)
+    # stitched state of 2 ranks (2 -> 4) or 3 ranks (3 -> 2) has the same length: plain slicing
+    full = torch.arange(total, dtype=torch.float32)
+    opt.load_full_state(7, full.to(torch.int16), full, full * 2)
+    assert opt.step_count == 7 and torch.equal(opt.m, full) and torch.equal(opt.v, full * 2)
+    # a shorter vector (less tail padding when it was saved): the missing tail is zero
+    short = full[: total - 1536]
+    opt.load_full_state(8, short.to(torch.int16), short, short)
+    assert torch.equal(opt.m[: total - 1536], short) and float(opt.m[total - 1536:].abs().sum()) == 0.0
+    # a longer vector (more tail padding): the surplus is dropped
+    longer = torch.cat([full, torch.zeros(4096)])
+    opt.load_full_state(9, longer.to(torch.int16), longer, longer)
+    assert torch.equal(opt.m, full)
 
 
 def test_split_master_is_exact():

@@ -72,7 +72,7 @@ def bench_gemm(M, N, K, a_t=False, b_t=False, compare=True):
     return rec
 
 
-def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True):
+def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True, iters=5, warmup=3):
     from zenyx_b200.ops import _ext
 
     C = _ext.C()
@@ -83,7 +83,8 @@ def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, S, device="cuda", dtype=torch.float32)
     scale = 1.0 / math.sqrt(D)
-    ms_f = time_cuda(lambda: C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False, 0, 0, 0), iters=5)
+    ms_f = time_cuda(lambda: C.attn_fwd(q, k, v, o, lse, scale, causal, 0, 0, [0], [0], False, 0, 0, 0), iters=iters,
+                     warmup=warmup)
     _ext.check_status()
     flops_f = 4.0 * B * Hq * S * S * D * (0.5 if causal else 1.0)
     rec = {"kernel": "attn_fwd", "S": S, "Hq": Hq, "Hkv": Hkv, "B": B, "causal": causal, "ms": round(ms_f, 3),
@@ -96,7 +97,7 @@ def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True):
         dk = torch.zeros(B, S, Hkv, D, device="cuda")
         dv = torch.zeros(B, S, Hkv, D, device="cuda")
         ms_b = time_cuda(lambda: C.attn_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scale, causal, 0, 0, [0], [0],
-                                            True, False, 0, 0, 0), iters=5)
+                                            True, False, 0, 0, 0), iters=iters, warmup=warmup)
         _ext.check_status()
         flops_b = 2.5 * flops_f
         out.append({"kernel": "attn_bwd", "S": S, "Hq": Hq, "Hkv": Hkv, "B": B, "causal": causal,
@@ -111,6 +112,9 @@ def main(argv=None):
     ap.add_argument("--no-attn", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--no-bwd", action="store_true")
+    ap.add_argument("--seq", type=int, nargs="*", default=None, help="attention sequence lengths (default 8192 32768)")
+    ap.add_argument("--attn-iters", type=int, default=5, help="timed attention launches (1 for a profiler capture)")
+    ap.add_argument("--attn-warmup", type=int, default=3)
     args = ap.parse_args(argv)
     shapes = [(8192, 8192, 8192, False, False)]
     if not args.quick:
@@ -124,8 +128,8 @@ def main(argv=None):
     for M, N, K, at, bt in ([] if args.no_gemm else shapes):
         print(json.dumps(bench_gemm(M, N, K, at, bt)), flush=True)
     if not args.no_attn:
-        for S in ([8192] if args.quick else [8192, 32768]):
-            for rec in bench_attn(S, bwd=not args.no_bwd):
+        for S in (args.seq or ([8192] if args.quick else [8192, 32768])):
+            for rec in bench_attn(S, bwd=not args.no_bwd, iters=args.attn_iters, warmup=args.attn_warmup):
                 print(json.dumps(rec), flush=True)
 
 

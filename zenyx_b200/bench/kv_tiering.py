@@ -10,8 +10,8 @@ acquires the block through ``BeladyKVCacheTieringManager.acquire`` and runs the 
 forward kernel of ``--q-tokens`` queries against it, so host-to-device copies overlap real tensor-core
 work. One JSON line: step time (CUDA events), exposed stall (host-measured waits on copies that had
 not landed), bytes per tier, hit rate, and the miss count an LRU policy takes on the same trace.
-The reference plans the same accesses in Python and never executes them
-(zenyx/train/belayd_kv_cache_tiering.py:44-260 in its source tree; the module is not in its wheel).
+The reference only describes this component (README.md:150-154); its stock tier manager is
+``KVTierManager`` (zenyx/streaming/kv_tiering.py:36-66), a capacity-ordered placement without a schedule.
 """
 from __future__ import annotations
 

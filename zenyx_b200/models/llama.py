@@ -118,7 +118,9 @@ class FlatBuffers:
     """The flat bf16 parameter buffer and the flat fp32 gradient buffer of a model.
 
     Parameters that take weight decay are laid out first; every tensor starts on a 256-byte
-    boundary; the total is padded to a multiple of ``align`` so it splits evenly into shards.
+    boundary; the total is padded to a multiple of ``align * 840`` (840 = lcm(1..8)), which does NOT
+    depend on the world size, so the same flat layout splits evenly into 4-aligned shards for any
+    rank count that divides it (1-8, 10, 12, 14, 16, ...) and a checkpoint re-shards across world sizes.
     With ``symmetric_group`` the two buffers live in peer-visible memory (needed by the fused
     reduce-scatter / AdamW / all-gather kernel when there is more than one rank).
     """
@@ -135,8 +137,10 @@ class FlatBuffers:
             off += (n + 127) // 128 * 128
             if decay:
                 self.decay_end = off
-        step = align * max(world_size, 1)
+        step = align * 840
         self.total = (off + step - 1) // step * step
+        if self.total % (4 * max(world_size, 1)) != 0:
+            raise ValueError(f"world size {world_size} does not divide the flat buffer into 4-aligned shards")
         self.sym_params = self.sym_grads = None
         dev = torch.device(device)
         if symmetric_group is not None and world_size > 1 and dev.type == "cuda":

@@ -154,12 +154,16 @@ class ZeroAdamW:
         self.v.copy_(sd["v"])
 
     def load_full_state(self, step: int, p_lo: torch.Tensor, m: torch.Tensor, v: torch.Tensor) -> None:
-        """Loads from unsharded state vectors [flat.total] (used when the world size changed)."""
+        """Loads from unsharded state vectors (used when the world size changed). A vector saved under an
+        older layout may be shorter or longer than ``flat.total``: the difference is tail padding, which
+        carries no parameter, so it is zero-filled or dropped."""
         lo, hi = self.shard_begin, self.shard_begin + self.n_shard
         self.step_count = int(step)
-        self.p_lo.copy_(p_lo[lo:hi])
-        self.m.copy_(m[lo:hi])
-        self.v.copy_(v[lo:hi])
+        for dst, src in ((self.p_lo, p_lo), (self.m, m), (self.v, v)):
+            piece = src[lo: min(hi, src.numel())]
+            dst[: piece.numel()].copy_(piece)
+            if piece.numel() < dst.numel():
+                dst[piece.numel():].zero_()
 
     def close(self) -> None:
         if self.barrier is not None:

@@ -9,8 +9,8 @@ ZENYX_2_0_DELIVERABLES.txt:190). The two conventions it leaves behind are honour
   (examples/03_expert_tpu_v5e8_training.py:206-218)  ->  ``export_pt``.
 
 Optimizer state is sharded: ``optim_rank<r>of<W>.safetensors`` holds that rank's slice of the fp32
-master remainder, m and v plus its shard bounds; ``meta.json`` carries step, config, curriculum
-state, RNG state and metrics. Files are written under a temporary name and renamed; a ``latest``
+master remainder, m and v plus its shard bounds; ``rng_rank<r>of<W>.json`` that rank's CPU RNG state;
+``meta.json`` carries step, config, curriculum state, rank 0's RNG state and metrics. Files are written under a temporary name and renamed; a ``latest``
 file points at the last complete step. Resume is bit-exact at the same world size, and valid across
 world-size changes (the shards are re-partitioned from the per-rank files).
 """
@@ -18,7 +18,6 @@ from __future__ import annotations
 
 import json
 import os
-import threading
 from typing import Any, Dict, Optional
 
 import torch
@@ -54,35 +53,30 @@ def model_state(model) -> Dict[str, torch.Tensor]:
 
 
 def save(ckpt_dir: str, step: int, model, optimizer=None, scheduler_state: Optional[Dict[str, Any]] = None,
-         config: Optional[Dict[str, Any]] = None, metrics: Optional[Dict[str, Any]] = None,
-         async_write: bool = False) -> str:
-    """Writes ``<ckpt_dir>/step_<step>/``. Every rank writes its optimizer shard; rank 0 writes the
-    model, the metadata and, last, the ``latest`` pointer. Returns the step directory."""
+         config: Optional[Dict[str, Any]] = None, metrics: Optional[Dict[str, Any]] = None) -> str:
+    """Writes ``<ckpt_dir>/step_<step>/`` synchronously. Every rank writes its optimizer shard and its own
+    RNG state; rank 0 writes the model, the metadata and, last, the ``latest`` pointer. Returns the step
+    directory."""
     rank, world = _rank_world()
     d = os.path.join(ckpt_dir, f"step_{step}")
     os.makedirs(d, exist_ok=True)
 
-    def work():
-        if optimizer is not None and hasattr(optimizer, "state_dict") and hasattr(optimizer, "n_shard"):
-            sd = optimizer.state_dict()
-            _atomic_save_tensors(os.path.join(d, f"optim_rank{rank}of{world}.safetensors"),
-                                 {"p_lo": sd["p_lo"], "m": sd["m"], "v": sd["v"]},
-                                 {"step": str(sd["step"]), "shard_begin": str(sd["shard_begin"]),
-                                  "n_shard": str(sd["n_shard"]), "world": str(world)})
-        elif optimizer is not None and rank == 0:
-            torch.save(optimizer.state_dict(), os.path.join(d, "optimizer.pt"))
-        if rank == 0:
-            _atomic_save_tensors(os.path.join(d, "model.safetensors"), model_state(model))
-            meta = {"step": step, "world_size": world, "config": config or {}, "metrics": metrics or {},
-                    "scheduler": scheduler_state or {}, "torch_rng": torch.get_rng_state().tolist()}
-            _atomic_write_bytes(os.path.join(d, "meta.json"), json.dumps(meta, default=str).encode())
+    if optimizer is not None and hasattr(optimizer, "state_dict") and hasattr(optimizer, "n_shard"):
+        sd = optimizer.state_dict()
+        _atomic_save_tensors(os.path.join(d, f"optim_rank{rank}of{world}.safetensors"),
+                             {"p_lo": sd["p_lo"], "m": sd["m"], "v": sd["v"]},
+                             {"step": str(sd["step"]), "shard_begin": str(sd["shard_begin"]),
+                              "n_shard": str(sd["n_shard"]), "world": str(world)})
+    elif optimizer is not None and rank == 0:
+        torch.save(optimizer.state_dict(), os.path.join(d, "optimizer.pt"))
+    if rank == 0:
+        _atomic_save_tensors(os.path.join(d, "model.safetensors"), model_state(model))
+        meta = {"step": step, "world_size": world, "config": config or {}, "metrics": metrics or {},
+                "scheduler": scheduler_state or {}, "torch_rng": torch.get_rng_state().tolist()}
+        _atomic_write_bytes(os.path.join(d, "meta.json"), json.dumps(meta, default=str).encode())
 
-    if async_write:
-        t = threading.Thread(target=work, daemon=False)
-        t.start()
-        t.join()  # tensors were snapshotted to host inside work(); joining keeps ordering simple and safe
-    else:
-        work()
+    _atomic_write_bytes(os.path.join(d, f"rng_rank{rank}of{world}.json"),
+                        json.dumps({"torch_rng": torch.get_rng_state().tolist()}).encode())
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -122,7 +116,10 @@ def load(ckpt_dir: str, model, optimizer=None, step: Optional[int] = None, stric
                                       full["p_lo"], full["m"], full["v"])
     elif optimizer is not None and os.path.exists(os.path.join(d, "optimizer.pt")):
         optimizer.load_state_dict(torch.load(os.path.join(d, "optimizer.pt"), map_location="cpu"))
-    if "torch_rng" in meta:
+    own_rng = os.path.join(d, f"rng_rank{rank}of{world}.json")
+    if os.path.exists(own_rng):      # same world size: every rank continues its own random stream
+        torch.set_rng_state(torch.tensor(json.loads(open(own_rng).read())["torch_rng"], dtype=torch.uint8))
+    elif "torch_rng" in meta:        # re-partitioned run: rank 0's stream is the only common reference
         torch.set_rng_state(torch.tensor(meta["torch_rng"], dtype=torch.uint8))
     return meta
 

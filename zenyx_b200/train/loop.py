@@ -32,6 +32,9 @@ def run(trainer: Trainer, data_iter: Iterable, criterion=None, cfg: Optional[Loo
         on_step: Optional[Callable[[int, Dict[str, Any]], None]] = None, watchdog=None) -> List[Dict[str, Any]]:
     """Runs ``cfg.steps`` optimizer steps; returns the per-step records.
 
+    ``data_iter`` yields the batches of the WHOLE run from step 0; on resume from step ``s`` its first
+    ``s`` batches are drawn and dropped, so the resumed run sees the batches an uninterrupted one would.
+
     ``watchdog`` is an optional ``zenyx_b200.core.distributed.Heartbeat``: it is beaten every step
     and, when it reports a dead peer, the loop stops before the next launch and raises.
     """
@@ -50,6 +53,8 @@ def run(trainer: Trainer, data_iter: Iterable, criterion=None, cfg: Optional[Loo
     records: List[Dict[str, Any]] = []
     sink = open(cfg.metrics_path, "a") if (cfg.metrics_path and rank == 0) else None
     it = iter(data_iter)
+    for _ in range(start):      # a resumed run continues the batch stream where the checkpoint left it
+        next(it)
     try:
         for step in range(start, cfg.steps):
             if watchdog is not None:

@@ -91,7 +91,8 @@ class Trainer:
             if cur is not None:
                 self.engine.set_ring_degree(cur.degree_at(self.step))
             local = self.engine.train_step(batch, target, lr=self._lr())
-            loss = self.engine.global_loss(local)
+            loss = self.engine.global_loss(local)       # reads the loss back: the step's kernels have finished
+            self._raise_on_kernel_error()
             if cur is not None:
                 cur.step(loss)
             self.step += 1
@@ -130,6 +131,17 @@ class Trainer:
         self.step += 1
         self.memory.snapshot()
         return float(reduced.item() / get_world_size())
+
+    def _raise_on_kernel_error(self) -> None:
+        """Reads the device status word that the kernels' bounded waits write when they give up (a peer
+        that never raised its flag, a barrier that ran out). Raises ``KernelError`` so that the caller, or
+        ``train.elastic.run_elastic``, stops instead of training on from a half-reduced update. Called where
+        the step has already synchronised, so it costs one 16-byte read."""
+        if self.ctx.device.type != "cuda":
+            return
+        from ..ops import _ext
+
+        _ext.check_status()
 
     def fit(self, data_iter: Iterable, criterion: Optional[nn.Module] = None, steps: int = 1) -> List[float]:
         losses: List[float] = []
