@@ -1,13 +1,14 @@
 // Flash-attention forward for sm_100a (head_dim 128, bf16 in, fp32 softmax/accumulate).
 //
 // One CTA owns two adjacent 128-row Q tiles of one head and walks the KV buffer once:
-//   warp 8      TMA producer: Q once, then K/V tiles through a 2-stage ring (plain per-CTA loads)
-//   warp 9      MMA issuer:   S_i = Q_i K^T  (SS form) and O_i += P_i V (A = P read from TMEM)
-//   warp 10     optional peer pull: copies this CTA's slice of the next ring step's K/V from the
-//               owning GPU into local staging with plain P2P loads while the tiles compute
-//   warps 0-3   softmax of Q tile 0, one thread per row, S/P/O live in TMEM
-//   warps 4-7   softmax of Q tile 1
-// The two softmax groups ping-pong so the tensor core always has the other tile's MMAs to run.
+//   warps 0-3    softmax of Q tile 0, one thread per row; S/P/O live in TMEM
+//   warps 4-7    softmax of Q tile 1
+//   warp 8       TMA producer: Q once, then K/V tiles through a 2-stage ring (plain per-CTA loads)
+//   warps 9, 10  MMA issuers, one per Q tile: S_i = Q_i K^T (SS form) and O_i += P_i V (A = P read from
+//                TMEM, issued in two halves so that it starts while the softmax finishes the row)
+//   warp 11      optional peer pull: copies this CTA's slice of the next ring step's K/V from the owning
+//                GPU into local staging with plain P2P loads while the tiles compute
+// The two Q tiles ping-pong so the tensor core has the other tile's MMAs to run during a softmax.
 // TMEM (512 columns): S0 | S1 | O0 | O1, with the bf16 P_i written over the first half of S_i.
 // O is only rescaled when a row's running max grew by more than 2^8 (the final 1/l makes the
 // result exact either way). Causal / block-sparse masks come from global token positions, so the
@@ -29,10 +30,20 @@ constexpr int BKV = 128;
 constexpr int TILE_BYTES = BQ * HD * 2;   // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk: 128 rows x 128 B
 constexpr int KV_STAGES = 2;
-constexpr int TMA_WARP = 16, MMA_WARP = 17, PULL_WARP = 18;
-constexpr int NUM_THREADS = 19 * 32;  // 16 softmax warps + TMA + MMA + peer-pull warp
+// Optional in-kernel timeline (compile with -DZX_FWD_TRACE): block 0 stamps the SM clock at the pipeline events
+// of its first 256 KV tiles into a device array that zx_fwd_trace_read() copies out. Not part of normal builds.
+#ifdef ZX_FWD_TRACE
+__device__ long long g_fwd_trace[256 * 32];
+#define ZX_TR(slot, iter) \
+  do { if (blockIdx.x == 0 && lane == 0 && (iter) < 256u) g_fwd_trace[(iter) * 32 + (slot)] = clock64(); } while (0)
+#else
+#define ZX_TR(slot, iter) do { } while (0)
+#endif
+
+constexpr int TMA_WARP = 8, MMA_WARP0 = 9, MMA_WARP1 = 10, PULL_WARP = 11;
+constexpr int NUM_THREADS = 12 * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256 + 2 * 2 * 2 * 128 * 4;
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 512;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
@@ -53,24 +64,9 @@ struct FwdParams {
   Status* status;
 };
 
-__device__ __forceinline__ bool tile_allowed(const FwdParams& p, int qpos0, int kpos0) {
-  if (p.causal && kpos0 > qpos0) return false;  // tiles are 128-aligned in position space
-  if (p.window_blocks > 0) {
-    const int qb = qpos0 >> 7, kb = kpos0 >> 7;
-    const int dist = qb >= kb ? qb - kb : kb - qb;
-    const bool in_window = dist < p.window_blocks;
-    const bool is_global = p.global_every > 0 && (kb % p.global_every) == 0;
-    if (!in_window && !is_global) return false;
-  }
-  return true;
-}
 __device__ __forceinline__ int q_tile_pos(const FwdParams& p, int t) {
   return p.q_chunk_pos[t / p.q_tiles_per_chunk] + (t % p.q_tiles_per_chunk) * BQ;
 }
-__device__ __forceinline__ int kv_tile_pos(const FwdParams& p, int j) {
-  return p.kv_chunk_pos[j / p.kv_tiles_per_chunk] + (j % p.kv_tiles_per_chunk) * BKV;
-}
-
 // warp-uniform bounded wait
 __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const bool ok = mbar_wait(bar, parity, abort_flag);
@@ -78,11 +74,11 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volati
 }
 
 // Rare path of the softmax warps (a row's running maximum grew by more than the threshold): multiply this
-// thread's 64 output columns by alpha in TMEM. Kept out of line so that its 32 extra live registers cost the
-// hot loop nothing; the call's register saves only happen when the branch is taken.
-__device__ __noinline__ void rescale_o_half(uint32_t o_tmem, float alpha) {
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
+// thread's output row by alpha in TMEM. Kept out of line so that its registers cost the hot loop nothing; the
+// call's register saves only happen when the branch is taken.
+__device__ __noinline__ void rescale_o_row(uint32_t o_tmem, float alpha) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
     uint32_t orow[32];
     tmem_ld_32x32b_x32(o_tmem + c * 32, orow);
     tmem_wait_ld();
@@ -90,6 +86,27 @@ __device__ __noinline__ void rescale_o_half(uint32_t o_tmem, float alpha) {
     for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
     tmem_st_32x32b_x32(o_tmem + c * 32, orow);
   }
+}
+
+// Plain scan over the KV tiles with the position kept incrementally (no division per tile).
+struct DenseWalk {
+  int j, kpos0, left_in_chunk, c;
+  __device__ __forceinline__ void init(const FwdParams& p) {
+    j = 0; c = 0; kpos0 = p.kv_chunk_pos[0]; left_in_chunk = p.kv_tiles_per_chunk;
+  }
+  __device__ __forceinline__ void next(const FwdParams& p) {
+    ++j;
+    kpos0 += BKV;
+    if (--left_in_chunk == 0) {
+      ++c;
+      left_in_chunk = p.kv_tiles_per_chunk;
+      kpos0 = p.kv_chunk_pos[c < kAttnMaxChunks ? c : 0];
+    }
+  }
+};
+// tile_allowed() for the dense instantiation (no window).
+__device__ __forceinline__ bool dense_allowed(const FwdParams& p, int qpos0, int kpos0) {
+  return !(p.causal && kpos0 > qpos0);
 }
 
 #define ZX_FWD_SPARSE 0
@@ -111,6 +128,12 @@ CUtensorMap make_qkv_map(const void* base, int B, int S, int H, int64_t tok_stri
 }
 
 }  // namespace
+
+#ifdef ZX_FWD_TRACE
+extern "C" int zx_fwd_trace_read(long long* host_dst) {
+  return (int)cudaMemcpyFromSymbol(host_dst, g_fwd_trace, sizeof(long long) * 256 * 32);
+}
+#endif
 
 void check_attn_common(int Hq, int Hkv, int Sq, int Skv, const AttnLayout& ql, const AttnLayout& kl) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) throw std::runtime_error("attention: Hq must be a multiple of Hkv");

@@ -66,6 +66,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+#ifdef ZX_ARRIVE_SYNC
+  __syncwarp();
+#endif
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
@@ -97,6 +100,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 #pragma unroll 1
   for (int i = 0; i < 1024; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef ZX_WAIT_SLEEP
+    __nanosleep(ZX_WAIT_SLEEP);
+#endif
   }
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
@@ -257,6 +263,96 @@ __device__ __forceinline__ void umma_commit_w(uint64_t* bar) {
       "elect.sync _|e, 0xffffffff;\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
       "}\n" ::"r"(smem_u32(bar))
+      : "memory");
+}
+// Eight MMAs of one 128 x N x 128 product (K = 8 x 16) in ONE asm statement: one election, the per-step
+// descriptor offsets as immediates. The issuing warp's instruction stream is on the critical path of the
+// attention kernels (it competes for issue slots with the softmax warps of its scheduler), so the cost per
+// MMA has to stay at a few instructions.
+//  K-major operand stored as two 64-element halves (HALF16 = distance of the halves in 16-byte units):
+//    step k starts at (k / 4) * HALF16 + (k % 4) * 2
+//  MN-major operand (rows = K index, 128 bytes per row): step k starts at k * 16 rows = k * 128 units.
+template <int HALF16>
+__device__ __forceinline__ void umma_ss_k8_kmajor_w(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                    uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e, p, t;\n\t"
+      ".reg .b64 a, b;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "add.s64 a, %1, 2;\n\t add.s64 b, %2, 2;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.s64 a, %1, 4;\n\t add.s64 b, %2, 4;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.s64 a, %1, 6;\n\t add.s64 b, %2, 6;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.s64 a, %1, %5;\n\t add.s64 b, %2, %5;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.s64 a, %1, %6;\n\t add.s64 b, %2, %6;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.s64 a, %1, %7;\n\t add.s64 b, %2, %7;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.s64 a, %1, %8;\n\t add.s64 b, %2, %8;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first), "n"(HALF16), "n"(HALF16 + 2), "n"(HALF16 + 4),
+      "n"(HALF16 + 6)
+      : "memory");
+}
+// A (M x 128 bf16, two values per 32-bit column) read from TMEM, B MN-major in shared memory.
+__device__ __forceinline__ void umma_ts_k8_mnmajor_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e, p, t;\n\t"
+      ".reg .b32 ta;\n\t"
+      ".reg .b64 b;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "add.u32 ta, %1, 8;\n\t add.s64 b, %2, 128;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 16;\n\t add.s64 b, %2, 256;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 24;\n\t add.s64 b, %2, 384;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 32;\n\t add.s64 b, %2, 512;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 40;\n\t add.s64 b, %2, 640;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 48;\n\t add.s64 b, %2, 768;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 56;\n\t add.s64 b, %2, 896;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+// Half of the above: four MMAs (K = 4 x 16 = 64), so that P V can start on the first 64 probabilities of a
+// row block while the softmax warps still work on the other 64.
+__device__ __forceinline__ void umma_ts_k4_mnmajor_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e, p, t;\n\t"
+      ".reg .b32 ta;\n\t"
+      ".reg .b64 b;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "add.u32 ta, %1, 8;\n\t add.s64 b, %2, 128;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 16;\n\t add.s64 b, %2, 256;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "add.u32 ta, %1, 24;\n\t add.s64 b, %2, 384;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc_first)
       : "memory");
 }
 // Warp-uniform bounded wait: every lane polls, the verdict is shared.
@@ -435,7 +531,9 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 // Pair exponential; every fourth pair (by the caller's compile-time index) takes the FMA pipe.
 template <int kIndex>
 __device__ __forceinline__ float2 exp2_pair(float2 x) {
+#ifndef ZX_NO_POLY
   if ((kIndex & 3) == 3) return exp2_poly2(x);
+#endif
   return make_float2(fast_exp2(x.x), fast_exp2(x.y));
 }
 

@@ -8,6 +8,7 @@ The reference project has no native code, hence no counterpart of this module.
 from __future__ import annotations
 
 import importlib.util
+import os
 import threading
 from pathlib import Path
 
@@ -26,7 +27,9 @@ def _load(name: str):
     with _lock:
         if name in _mods:
             return _mods[name]
-        path = _PKG / f"{name}.so"
+        # ZENYX_B200_EXT_DIR: take the extensions from another directory (a build made with other
+        # compile-time options, for A/B measurements); by default the in-tree build next to the package.
+        path = Path(os.environ.get("ZENYX_B200_EXT_DIR", str(_PKG))) / f"{name}.so"
         if not path.exists():
             raise RuntimeError(
                 f"zenyx_b200: native extension {path} is missing; run `python -m zenyx_b200._build` "
