@@ -34,6 +34,13 @@ constexpr int W_TMA = 8, W_MMA = 9;        // dQ kernel roles (the dK/dV kernel 
 constexpr int N_COMPUTE = 256;             // compute threads
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
+// Every BWD_POLY_EVERY-th pair of exponentials can be evaluated as a polynomial on the FMA pipe instead of the
+// special-function unit. Measured: these kernels are bound by instruction issue and by their dependency
+// chain, not by that unit, and the polynomial's extra instructions cost as much as they save (29.1 ms with
+// every second pair, 28.4 ms with none at S = 32768), so the default is none.
+#ifndef BWD_POLY_EVERY
+#define BWD_POLY_EVERY 1000000
+#endif
 
 struct BwdParams {
   int B, Hq, Hkv, Sq, Skv;
@@ -56,20 +63,22 @@ struct BwdParams {
   Status* status;
 };
 
-// clock stamp of one pipeline event (dQ kernel, first CTA only, when a trace buffer is given)
+// Clock stamps of pipeline events into the caller's trace buffer (first CTA of each kernel). Compiled in only
+// with -DZX_BWD_TRACE: the stamps cost issue slots in loops that are bound by instruction issue.
+#ifdef ZX_BWD_TRACE
 #define ZX_TRACE_DKDV(iter, slot)                                                     \
   do {                                                                                \
     if (p.trace != nullptr && blockIdx.x == 0 && (iter) < 64) p.trace[1024 + (iter) * 16 + (slot)] = clock64(); \
-  } while (0)
-#define ZX_TRACE_W(iter, k)                                                           \
-  do {                                                                                \
-    if (p.trace != nullptr && blockIdx.x == 0 && lane == 0 && warp < 8 && (iter) >= 8 && (iter) < 24)                      \
-      p.trace[2048 + (((iter) - 8) * 8 + warp) * 8 + (k)] = clock64();                                          \
   } while (0)
 #define ZX_TRACE(iter, slot)                                                          \
   do {                                                                                \
     if (p.trace != nullptr && blockIdx.x == 0 && (iter) < 64) p.trace[(iter) * 16 + (slot)] = clock64(); \
   } while (0)
+#else
+#define ZX_TRACE_DKDV(iter, slot) do { } while (0)
+#define ZX_TRACE(iter, slot) do { } while (0)
+#endif
+#define ZX_TRACE_W(iter, k) do { } while (0)
 
 __device__ __forceinline__ int q_tile_pos(const BwdParams& p, int t) {
   return p.q_chunk_pos[t / p.q_tiles_per_chunk] + (t % p.q_tiles_per_chunk) * BT;
@@ -77,6 +86,53 @@ __device__ __forceinline__ int q_tile_pos(const BwdParams& p, int t) {
 __device__ __forceinline__ int kv_tile_pos(const BwdParams& p, int j) {
   return p.kv_chunk_pos[j / p.kv_tiles_per_chunk] + (j % p.kv_tiles_per_chunk) * BT;
 }
+// The Q tiles that may attend the KV tile at position kpos0, in order. The backward kernels are bound by
+// instruction issue, and every role of a CTA walks this sequence once per item, so the dense instantiation
+// keeps the position incrementally (no division, no search); windowed masks use the jumping search.
+template <bool SPARSE>
+struct QWalk {
+  int t, qpos0, in_chunk, c;
+  __device__ __forceinline__ void init() { t = -1; qpos0 = 0; in_chunk = 0; c = 0; }
+  __device__ __forceinline__ bool next(const BwdParams& p, int kpos0) {
+    if constexpr (SPARSE) {
+      t = next_q_tile(p, kpos0, t + 1);
+      if (t >= p.n_q_tiles) return false;
+      qpos0 = q_tile_pos(p, t);
+      return true;
+    } else {
+      for (;;) {
+        if (++t >= p.n_q_tiles) return false;
+        if (in_chunk == p.q_tiles_per_chunk) { ++c; in_chunk = 0; }
+        qpos0 = p.q_chunk_pos[c] + in_chunk * BT;
+        ++in_chunk;
+        if (!(p.causal && kpos0 > qpos0)) return true;
+      }
+    }
+  }
+};
+// The KV tiles the Q tile at position qpos0 may attend, in order.
+template <bool SPARSE>
+struct KvWalk {
+  int j, kpos0, in_chunk, c;
+  __device__ __forceinline__ void init() { j = -1; kpos0 = 0; in_chunk = 0; c = 0; }
+  __device__ __forceinline__ bool next(const BwdParams& p, int qpos0) {
+    if constexpr (SPARSE) {
+      j = next_kv_tile(p, qpos0, j + 1);
+      if (j >= p.n_kv_tiles) return false;
+      kpos0 = kv_tile_pos(p, j);
+      return true;
+    } else {
+      for (;;) {
+        if (++j >= p.n_kv_tiles) return false;
+        if (in_chunk == p.kv_tiles_per_chunk) { ++c; in_chunk = 0; }
+        kpos0 = p.kv_chunk_pos[c] + in_chunk * BT;
+        ++in_chunk;
+        if (!(p.causal && kpos0 > qpos0)) return true;
+      }
+    }
+  }
+};
+
 __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const bool ok = mbar_wait(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
@@ -92,12 +148,6 @@ __device__ __forceinline__ uint64_t base_kmajor(uint32_t tile_addr) { return mak
 __device__ __forceinline__ uint64_t base_mnmajor(uint32_t tile_addr) {
   return make_smem_desc_sw128(tile_addr, HALF_BYTES, 1024);
 }
-// ... and their k-step variants: one add each. K-major: 16 elements of d; MN-major: 16 token rows.
-__device__ __forceinline__ uint64_t desc_kmajor(uint64_t base, int k) {
-  return desc_advance(base, (k >> 2) * HALF_BYTES + (k & 3) * 32);
-}
-__device__ __forceinline__ uint64_t desc_mnmajor(uint64_t base, int k) { return desc_advance(base, k * 16 * 128); }
-
 // ------------------------------------------------------------------------------------------
 // delta[b, h, s] = sum_d dO * O
 // ------------------------------------------------------------------------------------------
@@ -141,6 +191,7 @@ constexpr int DKDV_SMEM =
     2 * TILE_BYTES /*K,V*/ + (Q_STAGES + DO_STAGES) * TILE_BYTES + DKDV_ALIGN_SLACK + DKDV_BAR_BYTES + DKDV_STAT_BYTES;
 static_assert(DKDV_SMEM <= 227 * 1024, "dK/dV kernel shared memory");
 
+template <bool SPARSE>
 __global__ void __launch_bounds__(DKDV_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdParams p) {
@@ -213,7 +264,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   // number of (head, q tile) items this CTA processes: identical in every role
   int n_items = 0;
-  for (int t = next_q_tile(p, kpos0, 0); t < p.n_q_tiles; t = next_q_tile(p, kpos0, t + 1)) ++n_items;
+  {
+    QWalk<SPARSE> w;
+    for (w.init(); w.next(p, kpos0);) ++n_items;
+  }
   n_items *= G;
 
   if (warp == KW_PULL) warp_pull_slice(p.pull_src, p.pull_dst, p.pull_nvec, lane);
@@ -233,7 +287,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         bool ok = true;
         for (int g = 0; g < G && ok; ++g) {
           const int hq = hk * G + g;
-          for (int t = next_q_tile(p, kpos0, 0); t < p.n_q_tiles; t = next_q_tile(p, kpos0, t + 1)) {
+          QWalk<SPARSE> w;
+          for (w.init(); w.next(p, kpos0);) {
+            const int t = w.t;
             const int qs = n % Q_STAGES, ds = n % DO_STAGES;
             if (!mbar_wait(&q_empty[qs], ((n / Q_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
             mbar_expect_tx(&q_full[qs], TILE_BYTES);
@@ -267,11 +323,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = ok && mbar_wait_w(&do_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(k_addr, k), desc_kmajor(q_k0, k), idesc_kk, k > 0);
+          umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, k_addr, q_k0, idesc_kk, 0u);
           umma_commit_w(s_full);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss_w(t_dp, desc_kmajor(v_addr, k), desc_kmajor(do_k0, k), idesc_kk, k > 0);
+          umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, v_addr, do_k0, idesc_kk, 0u);
           umma_commit_w(dp_full);
         }
         int n = 0;
@@ -287,38 +341,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (!mbar_wait_w(p_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           if (lane == 0) ZX_TRACE_DKDV(n, 8);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts_w(t_dv, t_s + (k >> 1) * 32 + (k & 1) * 8, desc_mnmajor(do_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_ts_k8_w<8, 32, 40, 64, 72, 96, 104>(t_dv, t_s, do_addr, idesc_tm, n > 0 ? 1u : 0u);
           umma_commit_w(&do_empty[ds]);   // dO(n) has now served dP^T(n) and dV(n)
           if (lane == 0) ZX_TRACE_DKDV(n, 9);
           if (has_next) {
             if (!mbar_wait_w(&q_full[qsn], ((n + 1) / Q_STAGES) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             if (lane == 0) ZX_TRACE_DKDV(n, 10);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(k_addr, k), desc_kmajor(qn_addr, k), idesc_kk, k > 0);
+            umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, k_addr, qn_addr, idesc_kk, 0u);
             umma_commit_w(s_full);
             if (lane == 0) ZX_TRACE_DKDV(n, 15);
-            if (p.trace != nullptr && blockIdx.x == 0) {
-              mbar_wait_w(s_full, (n + 1) & 1, abort_flag);
-              if (lane == 0) ZX_TRACE_DKDV(n, 14);
-            }
           }
           // dK += dS^T Q
           if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           if (lane == 0) ZX_TRACE_DKDV(n, 11);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts_w(t_dk, t_dp + (k >> 1) * 32 + (k & 1) * 8, desc_mnmajor(q_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_ts_k8_w<8, 32, 40, 64, 72, 96, 104>(t_dk, t_dp, q_addr, idesc_tm, n > 0 ? 1u : 0u);
           umma_commit_w(&q_empty[qs]);    // Q(n) has now served S^T(n) and dK(n)
           if (lane == 0) ZX_TRACE_DKDV(n, 12);
           if (has_next) {
             if (!mbar_wait_w(&do_full[dsn], ((n + 1) / DO_STAGES) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             if (lane == 0) ZX_TRACE_DKDV(n, 13);
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_ss_w(t_dp, desc_kmajor(v_addr, k), desc_kmajor(don_addr, k), idesc_kk, k > 0);
+            umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, v_addr, don_addr, idesc_kk, 0u);
             umma_commit_w(dp_full);
           }
         }
@@ -349,30 +394,34 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // sits between a TMEM read and its use. Buffer (n + 1) & 1 was last read in iteration
       // n - 1, and every thread finished that before dP^T(n) could be issued.
       const int ct = threadIdx.x;  // 0..255
+      // this thread's statistic of item (g, t): -lse * log2e of query ct for ct < 128, else -delta of query ct - 128
+      const float* stat_src = (ct < BT ? p.lse : p.delta) + ((size_t)b * p.Hq + (size_t)hk * G) * p.Sq + (ct & (BT - 1));
+      const float stat_mul = ct < BT ? -LOG2E : -1.f;
       auto stat_fetch = [&](int g, int t) -> float {
-        const size_t base = ((size_t)b * p.Hq + (hk * G + g)) * p.Sq + (size_t)t * BT;
-        return ct < BT ? -LOG2E * __ldg(p.lse + base + ct) : -__ldg(p.delta + base + (ct - BT));
+        return stat_mul * __ldg(stat_src + (size_t)g * p.Sq + (size_t)t * BT);
       };
-      auto next_item = [&](int& g, int& t) -> bool {
+      QWalk<SPARSE> walk;
+      auto next_item = [&](int& g) -> bool {   // advances walk (and g when a head's tiles are exhausted)
         for (;;) {
-          t = next_q_tile(p, kpos0, t + 1);
-          if (t < p.n_q_tiles) return true;
-          t = -1;
+          if (walk.next(p, kpos0)) return true;
+          walk.init();
           if (++g >= G) return false;
         }
       };
-      int g = 0, t = -1;
-      bool have = next_item(g, t);
+      int g = 0;
+      walk.init();
+      bool have = next_item(g);
+      int t = walk.t, qpos0 = walk.qpos0;
       if (have && ct < 256) {
         stats[ct] = stat_fetch(g, t);
         mbar_arrive_warp(&stat_ready[0]);
       }
       while (have) {
-        int gn = g, tn = t;
-        const bool have_next = next_item(gn, tn);
+        int gn = g;
+        const bool have_next = next_item(gn);
+        const int tn = walk.t, qposn = walk.qpos0;
         float pre = 0.f;
         if (have_next && ct < 256) pre = stat_fetch(gn, tn);
-        const int qpos0 = q_tile_pos(p, t);
         const float* st = stats + (n & 1) * 256;
         if (!wait_warp(&stat_ready[n & 1], (n >> 1) & 1, abort_flag)) { ok = false; break; }
         ZX_TRACE_W(n, 7);
@@ -388,18 +437,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int qp = qpos0 + col0;   // column c is query qp + c; it sees this key iff my_kpos <= qp + c
         const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
         const float4* nl4 = reinterpret_cast<const float4*>(st + col0);   // uniform address: broadcast reads
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
+        static_for<8>([&](auto idx4) {
+          constexpr int c4 = decltype(idx4)::value;
           const float4 nl = nl4[c4];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int c = 2 * c4 + h;
+          static_for<2>([&](auto idxh) {
+            constexpr int h = decltype(idxh)::value;
+            constexpr int c = 2 * c4 + h;
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2,
                                         h == 0 ? make_float2(nl.x, nl.y) : make_float2(nl.z, nl.w));
-            sr[2 * c] = __float_as_uint(fast_exp2(x.x));
-            sr[2 * c + 1] = __float_as_uint(fast_exp2(x.y));
-          }
-        }
+            const float2 e = exp2_pair<c, BWD_POLY_EVERY>(x);
+            sr[2 * c] = __float_as_uint(e.x);
+            sr[2 * c + 1] = __float_as_uint(e.y);
+          });
+        });
         if (diag) {   // only tiles on the diagonal pay for the per-element mask
 #pragma unroll
           for (int c = 0; c < 32; ++c)
@@ -454,6 +504,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         g = gn;
         t = tn;
+        qpos0 = qposn;
         have = have_next;
         ++n;
       }
@@ -504,6 +555,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int DQ_SMEM = 2 * TILE_BYTES /*Q,dO*/ + (K_STAGES + V_STAGES) * TILE_BYTES + 1024 + 256;
 
+template <bool SPARSE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdParams p) {
@@ -567,7 +619,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   int n_items = 0;
-  for (int j = next_kv_tile(p, qpos0, 0); j < p.n_kv_tiles; j = next_kv_tile(p, qpos0, j + 1)) ++n_items;
+  {
+    KvWalk<SPARSE> w;
+    for (w.init(); w.next(p, qpos0);) ++n_items;
+  }
 
   if (n_items > 0) {
     if (warp == W_TMA) {
@@ -581,7 +636,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_4d(sdO + HALF_BYTES, &tmdO, qdo_full, 64, hq, t * BT, b);
         uint32_t n = 0;
         bool ok = true;
-        for (int j = next_kv_tile(p, qpos0, 0); j < p.n_kv_tiles; j = next_kv_tile(p, qpos0, j + 1)) {
+        KvWalk<SPARSE> w;
+        for (w.init(); w.next(p, qpos0);) {
+          const int j = w.j;
           const int ks = n % K_STAGES, vs = n % V_STAGES;
           if (!mbar_wait(&k_empty[ks], ((n / K_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&k_full[ks], TILE_BYTES);
@@ -613,11 +670,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = ok && mbar_wait_w(&v_full[0], 0, abort_flag);
         tc_fence_after();
         if (ok) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(q_addr, k), desc_kmajor(k_k0, k), idesc_kk, k > 0);
+          umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, q_addr, k_k0, idesc_kk, 0u);
           umma_commit_w(s_full);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(v_k0, k), idesc_kk, k > 0);
+          umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, do_addr, v_k0, idesc_kk, 0u);
           umma_commit_w(dp_full);
           umma_commit_w(&v_empty[0]);
         }
@@ -632,23 +687,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (!mbar_wait_w(s_read, n & 1, abort_flag)) { ok = false; break; }
             if (!mbar_wait_w(&k_full[ksn], ((n + 1) / K_STAGES) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < 8; ++k) umma_ss_w(t_s, desc_kmajor(q_addr, k), desc_kmajor(kn_addr, k), idesc_kk, k > 0);
+            umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, q_addr, kn_addr, idesc_kk, 0u);
             umma_commit_w(s_full);
           }
           if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           if (lane == 0) ZX_TRACE(n, 8);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_ts_w(t_dq, t_dp + (k >> 2) * 64 + (k & 3) * 8, desc_mnmajor(k_addr, k), idesc_tm, (n > 0 || k > 0));
+          umma_ts_k8_w<8, 16, 24, 64, 72, 80, 88>(t_dq, t_dp, k_addr, idesc_tm, n > 0 ? 1u : 0u);
           umma_commit_w(&k_empty[ks]);    // K(n) has now served S(n) and dQ(n)
           if (lane == 0) ZX_TRACE(n, 9);
           if (has_next) {
             if (!mbar_wait_w(&v_full[vsn], ((n + 1) / V_STAGES) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_ss_w(t_dp, desc_kmajor(do_addr, k), desc_kmajor(vn_addr, k), idesc_kk, k > 0);
+            umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, do_addr, vn_addr, idesc_kk, 0u);
             umma_commit_w(dp_full);
             umma_commit_w(&v_empty[vsn]);   // V(n+1) is only read by dP(n+1)
           }
@@ -677,8 +728,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int my_qpos = qpos0 + r;
       uint32_t n = 0;
       bool ok = true;
-      for (int j = next_kv_tile(p, qpos0, 0); j < p.n_kv_tiles; j = next_kv_tile(p, qpos0, j + 1)) {
-        const int kpos0 = kv_tile_pos(p, j);
+      KvWalk<SPARSE> walk;
+      for (walk.init(); walk.next(p, qpos0);) {
+        const int kpos0 = walk.kpos0;
         if (!wait_warp(s_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (threadIdx.x == 0) ZX_TRACE(n, 0);
@@ -694,12 +746,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int kp = kpos0 + col0;
         const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
         const float2 nl2 = make_float2(-lse2, -lse2);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {   // packed fp32x2 math: two key columns per instruction
+        static_for<32>([&](auto idx) {   // packed fp32x2 math: two key columns per instruction
+          constexpr int c = decltype(idx)::value;
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2, nl2);
-          sr[2 * c] = __float_as_uint(fast_exp2(x.x));
-          sr[2 * c + 1] = __float_as_uint(fast_exp2(x.y));
-        }
+          const float2 e = exp2_pair<c, BWD_POLY_EVERY>(x);
+          sr[2 * c] = __float_as_uint(e.x);
+          sr[2 * c + 1] = __float_as_uint(e.y);
+        });
         if (diag) {   // only tiles on the diagonal pay for the per-element mask
 #pragma unroll
           for (int c = 0; c < 64; ++c)
@@ -822,12 +875,20 @@ void launch_attn_bwd(const AttnBwdArgs& a) {
   static PerDeviceOnce once;
   bool& configured = once.current();
   if (!configured) {
-    set_smem(attn_bwd_dkdv_kernel, DKDV_SMEM, "attn_bwd_dkdv");
-    set_smem(attn_bwd_dq_kernel, DQ_SMEM, "attn_bwd_dq");
+    set_smem(attn_bwd_dkdv_kernel<false>, DKDV_SMEM, "attn_bwd_dkdv");
+    set_smem(attn_bwd_dkdv_kernel<true>, DKDV_SMEM, "attn_bwd_dkdv (windowed)");
+    set_smem(attn_bwd_dq_kernel<false>, DQ_SMEM, "attn_bwd_dq");
+    set_smem(attn_bwd_dq_kernel<true>, DQ_SMEM, "attn_bwd_dq (windowed)");
     configured = true;
   }
-  attn_bwd_dkdv_kernel<<<p.n_kv_tiles * a.B * a.Hkv, DKDV_THREADS, DKDV_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
-  attn_bwd_dq_kernel<<<p.n_q_tiles * a.B * a.Hq, NUM_THREADS, DQ_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
+  const unsigned grid_kv = p.n_kv_tiles * a.B * a.Hkv, grid_q = p.n_q_tiles * a.B * a.Hq;
+  if (p.window_blocks > 0) {
+    attn_bwd_dkdv_kernel<true><<<grid_kv, DKDV_THREADS, DKDV_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
+    attn_bwd_dq_kernel<true><<<grid_q, NUM_THREADS, DQ_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
+  } else {
+    attn_bwd_dkdv_kernel<false><<<grid_kv, DKDV_THREADS, DKDV_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
+    attn_bwd_dq_kernel<false><<<grid_q, NUM_THREADS, DQ_SMEM, a.stream>>>(tmQ, tmdO, tmK, tmV, p);
+  }
 }
 
 }  // namespace zx

@@ -302,9 +302,12 @@ __device__ __forceinline__ void umma_ss_k8_kmajor_w(uint32_t d_tmem, uint64_t a_
       "n"(HALF16 + 6)
       : "memory");
 }
-// A (M x 128 bf16, two values per 32-bit column) read from TMEM, B MN-major in shared memory.
-__device__ __forceinline__ void umma_ts_k8_mnmajor_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                                     uint32_t acc_first) {
+// A (M x 128 bf16, two values per 32-bit column) read from TMEM, B MN-major in shared memory. A1..A7 are the
+// TMEM column offsets of K steps 1..7 relative to step 0 (8 columns per step when A is stored contiguously;
+// the backward kernels keep it in several column groups).
+template <int A1, int A2, int A3, int A4, int A5, int A6, int A7>
+__device__ __forceinline__ void umma_ts_k8_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t acc_first) {
   asm volatile(
       "{\n\t"
       ".reg .pred e, p, t;\n\t"
@@ -314,23 +317,27 @@ __device__ __forceinline__ void umma_ts_k8_mnmajor_w(uint32_t d_tmem, uint32_t a
       "setp.ne.b32 p, %4, 0;\n\t"
       "setp.eq.b32 t, %3, %3;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "add.u32 ta, %1, 8;\n\t add.s64 b, %2, 128;\n\t"
+      "add.u32 ta, %1, %5;\n\t add.s64 b, %2, 128;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
-      "add.u32 ta, %1, 16;\n\t add.s64 b, %2, 256;\n\t"
+      "add.u32 ta, %1, %6;\n\t add.s64 b, %2, 256;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
-      "add.u32 ta, %1, 24;\n\t add.s64 b, %2, 384;\n\t"
+      "add.u32 ta, %1, %7;\n\t add.s64 b, %2, 384;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
-      "add.u32 ta, %1, 32;\n\t add.s64 b, %2, 512;\n\t"
+      "add.u32 ta, %1, %8;\n\t add.s64 b, %2, 512;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
-      "add.u32 ta, %1, 40;\n\t add.s64 b, %2, 640;\n\t"
+      "add.u32 ta, %1, %9;\n\t add.s64 b, %2, 640;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
-      "add.u32 ta, %1, 48;\n\t add.s64 b, %2, 768;\n\t"
+      "add.u32 ta, %1, %10;\n\t add.s64 b, %2, 768;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
-      "add.u32 ta, %1, 56;\n\t add.s64 b, %2, 896;\n\t"
+      "add.u32 ta, %1, %11;\n\t add.s64 b, %2, 896;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], b, %3, t;\n\t"
       "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc_first)
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc_first), "n"(A1), "n"(A2), "n"(A3), "n"(A4), "n"(A5), "n"(A6), "n"(A7)
       : "memory");
+}
+__device__ __forceinline__ void umma_ts_k8_mnmajor_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t acc_first) {
+  umma_ts_k8_w<8, 16, 24, 32, 40, 48, 56>(d_tmem, a_tmem, b_desc, idesc, acc_first);
 }
 // Half of the above: four MMAs (K = 4 x 16 = 64), so that P V can start on the first 64 probabilities of a
 // row block while the softmax warps still work on the other 64.
@@ -528,11 +535,13 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   return make_float2(__int_as_float((__float_as_int(t.x) << 23) + __float_as_int(q.x)),
                      __int_as_float((__float_as_int(t.y) << 23) + __float_as_int(q.y)));
 }
-// Pair exponential; every fourth pair (by the caller's compile-time index) takes the FMA pipe.
-template <int kIndex>
+// Pair exponential; every kEvery-th pair (by the caller's compile-time index) takes the FMA pipe. Four suits a
+// loop whose FMA pipe is already busy (the forward softmax: row sums, packing); two suits the backward kernels,
+// whose exponential phase sits alone on the critical path with the FMA pipe nearly idle.
+template <int kIndex, int kEvery = 4>
 __device__ __forceinline__ float2 exp2_pair(float2 x) {
 #ifndef ZX_NO_POLY
-  if ((kIndex & 3) == 3) return exp2_poly2(x);
+  if ((kIndex % kEvery) == kEvery - 1) return exp2_poly2(x);
 #endif
   return make_float2(fast_exp2(x.x), fast_exp2(x.y));
 }
