@@ -1,11 +1,10 @@
 // Flash-attention forward for sm_100a (head_dim 128, bf16 in, fp32 softmax/accumulate).
 //
 // One CTA owns two adjacent 128-row Q tiles of one head and walks the KV buffer once:
-//   warps 0-3    softmax of Q tile 0, one thread per row; S/P/O live in TMEM
-//   warps 4-7    softmax of Q tile 1
+//   warps 0-7    softmax of BOTH Q tiles, one tile at a time: lane quarter = warp % 4, column half = warp / 4,
+//                two threads per score row; S/P/O live in TMEM
 //   warp 8       TMA producer: Q once, then K/V tiles through a 2-stage ring (plain per-CTA loads)
-//   warps 9, 10  MMA issuers, one per Q tile: S_i = Q_i K^T (SS form) and O_i += P_i V (A = P read from
-//                TMEM, issued in two halves so that it starts while the softmax finishes the row)
+//   warps 9, 10  MMA issuers, one per Q tile: S_i = Q_i K^T (SS form) and O_i += P_i V (A = P read from TMEM)
 //   warp 11      optional peer pull: copies this CTA's slice of the next ring step's K/V from the owning
 //                GPU into local staging with plain P2P loads while the tiles compute
 // The two Q tiles ping-pong so the tensor core has the other tile's MMAs to run during a softmax.
@@ -43,7 +42,7 @@ __device__ long long g_fwd_trace[256 * 32];
 constexpr int TMA_WARP = 8, MMA_WARP0 = 9, MMA_WARP1 = 10, PULL_WARP = 11;
 constexpr int NUM_THREADS = 12 * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 512;
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
@@ -74,11 +73,11 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volati
 }
 
 // Rare path of the softmax warps (a row's running maximum grew by more than the threshold): multiply this
-// thread's output row by alpha in TMEM. Kept out of line so that its registers cost the hot loop nothing; the
-// call's register saves only happen when the branch is taken.
-__device__ __noinline__ void rescale_o_row(uint32_t o_tmem, float alpha) {
+// thread's 64 output columns by alpha in TMEM. Kept out of line so that its registers cost the hot loop
+// nothing; the call's register saves only happen when the branch is taken.
+__device__ __noinline__ void rescale_o_half(uint32_t o_tmem, float alpha) {
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < 2; ++c) {
     uint32_t orow[32];
     tmem_ld_32x32b_x32(o_tmem + c * 32, orow);
     tmem_wait_ld();
