@@ -41,6 +41,12 @@ constexpr float LOG2E = 1.4426950408889634f;
 #ifndef BWD_POLY_EVERY
 #define BWD_POLY_EVERY 1000000
 #endif
+#ifndef DQ_POLY_EVERY
+#define DQ_POLY_EVERY BWD_POLY_EVERY
+#endif
+#ifndef DKDV_POLY_EVERY
+#define DKDV_POLY_EVERY BWD_POLY_EVERY
+#endif
 
 struct BwdParams {
   int B, Hq, Hkv, Sq, Skv;
@@ -445,7 +451,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             constexpr int c = 2 * c4 + h;
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2,
                                         h == 0 ? make_float2(nl.x, nl.y) : make_float2(nl.z, nl.w));
-            const float2 e = exp2_pair<c, BWD_POLY_EVERY>(x);
+            const float2 e = exp2_pair<c, DKDV_POLY_EVERY>(x);
             sr[2 * c] = __float_as_uint(e.x);
             sr[2 * c + 1] = __float_as_uint(e.y);
           });
@@ -749,7 +755,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         static_for<32>([&](auto idx) {   // packed fp32x2 math: two key columns per instruction
           constexpr int c = decltype(idx)::value;
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sl2, nl2);
-          const float2 e = exp2_pair<c, BWD_POLY_EVERY>(x);
+          const float2 e = exp2_pair<c, DQ_POLY_EVERY>(x);
           sr[2 * c] = __float_as_uint(e.x);
           sr[2 * c + 1] = __float_as_uint(e.y);
         });

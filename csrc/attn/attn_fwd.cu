@@ -1,10 +1,11 @@
 // Flash-attention forward for sm_100a (head_dim 128, bf16 in, fp32 softmax/accumulate).
 //
 // One CTA owns two adjacent 128-row Q tiles of one head and walks the KV buffer once:
-//   warps 0-7    softmax of BOTH Q tiles, one tile at a time: lane quarter = warp % 4, column half = warp / 4,
-//                two threads per score row; S/P/O live in TMEM
+//   warps 0-7    softmax of BOTH Q tiles, one tile at a time; warp (q, hf) owns 16 TMEM lanes (rows) and reads
+//                them in the accumulator-fragment layout; S/P/O live in TMEM
 //   warp 8       TMA producer: Q once, then K/V tiles through a 2-stage ring (plain per-CTA loads)
-//   warps 9, 10  MMA issuers, one per Q tile: S_i = Q_i K^T (SS form) and O_i += P_i V (A = P read from TMEM)
+//   warps 9, 10  MMA issuers, one per Q tile: S_i = Q_i K^T (SS form) and O_i += P_i V (A = P read from
+//                TMEM, issued in two halves so that it starts while the softmax finishes the row block)
 //   warp 11      optional peer pull: copies this CTA's slice of the next ring step's K/V from the owning
 //                GPU into local staging with plain P2P loads while the tiles compute
 // The two Q tiles ping-pong so the tensor core has the other tile's MMAs to run during a softmax.
@@ -73,18 +74,25 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volati
 }
 
 // Rare path of the softmax warps (a row's running maximum grew by more than the threshold): multiply this
-// thread's 64 output columns by alpha in TMEM. Kept out of line so that its registers cost the hot loop
-// nothing; the call's register saves only happen when the branch is taken.
-__device__ __noinline__ void rescale_o_half(uint32_t o_tmem, float alpha) {
+// thread's entries of the output rows by their row's alpha in TMEM (fragment layout: registers 4k, 4k+1 belong
+// to row a, 4k+2, 4k+3 to row b). Kept out of line so that its registers cost the hot loop nothing; the call's
+// register saves only happen when the branch is taken.
+__device__ __noinline__ void rescale_o_rows(uint32_t o_tmem, float alpha_a, float alpha_b) {
 #pragma unroll 1
   for (int c = 0; c < 2; ++c) {
-    uint32_t orow[32];
-    tmem_ld_32x32b_x32(o_tmem + c * 32, orow);
+    uint32_t x[32];
+    tmem_ld_16x256b_x8(o_tmem + c * 64, x);
     tmem_wait_ld();
 #pragma unroll
-    for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
-    tmem_st_32x32b_x32(o_tmem + c * 32, orow);
+    for (int k = 0; k < 8; ++k) {
+      x[4 * k] = __float_as_uint(__uint_as_float(x[4 * k]) * alpha_a);
+      x[4 * k + 1] = __float_as_uint(__uint_as_float(x[4 * k + 1]) * alpha_a);
+      x[4 * k + 2] = __float_as_uint(__uint_as_float(x[4 * k + 2]) * alpha_b);
+      x[4 * k + 3] = __float_as_uint(__uint_as_float(x[4 * k + 3]) * alpha_b);
+    }
+    tmem_st_16x256b_x8(o_tmem + c * 64, x);
   }
+  tmem_wait_st();
 }
 
 // Plain scan over the KV tiles with the position kept incrementally (no division per tile).
