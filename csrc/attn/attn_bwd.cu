@@ -29,8 +29,8 @@ constexpr int HD = 128;
 constexpr int BT = 128;                    // tile edge in tokens (both Q and KV)
 constexpr int TILE_BYTES = BT * HD * 2;    // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 64-wide d chunk
-constexpr int NUM_THREADS = 320;           // 8 compute warps (two warpgroups) + TMA warp + MMA warp
-constexpr int W_TMA = 8, W_MMA = 9;        // dQ kernel roles (the dK/dV kernel has its own, below)
+constexpr int NUM_THREADS = 352;           // dQ kernel: 8 compute warps (two warpgroups) + TMA warp + two MMA warps
+constexpr int W_TMA = 8, W_MMA = 9, W_MMA_DQ = 10;   // dQ kernel roles (the dK/dV kernel has its own, below)
 constexpr int N_COMPUTE = 256;             // compute threads
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -559,7 +559,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // K lives until dQ of its item has been issued, V only until dP: a 3-deep K ring and a 2-deep V
 // ring free every slot a full iteration before its next tile is needed (hides the TMA latency).
 constexpr int K_STAGES = 3, V_STAGES = 2;
-constexpr int DQ_SMEM = 2 * TILE_BYTES /*Q,dO*/ + (K_STAGES + V_STAGES) * TILE_BYTES + 1024 + 256;
+constexpr int DQ_SMEM = 2 * TILE_BYTES /*Q,dO*/ + (K_STAGES + V_STAGES) * TILE_BYTES + 1024 + 256;   // barriers: 21 x 8 B
 
 template <bool SPARSE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -582,8 +582,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* s_read = bars + 13;    // 1 (one arrival per compute warp)
   uint64_t* ds_ready = bars + 14;  // 1 (one arrival per compute warp)
   uint64_t* acc_done = bars + 15;  // 1
-  uint64_t* drain_bar = bars + 16; // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* drain_bar = bars + 16; // [2]
+  uint64_t* dp_free = bars + 18;   // [2] dQ of the item that used this dP buffer has finished reading it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -611,7 +612,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(s_read, N_COMPUTE / 32);    // per-warp arrivals
     mbar_init(ds_ready, N_COMPUTE / 32);
     mbar_init(acc_done, 1);
-    mbar_init(drain_bar, 1);
+    mbar_init(&drain_bar[0], 1);
+    mbar_init(&drain_bar[1], 1);
+    mbar_init(&dp_free[0], 1);
+    mbar_init(&dp_free[1], 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -664,60 +668,75 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     } else if (warp == W_MMA) {
-      {  // all 32 lanes run this loop; the instructions themselves are issued by one elected lane
-        constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);
-        constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);
-        const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
-        const uint64_t q_addr = base_kmajor(smem_u32(sQ)), do_addr = base_kmajor(smem_u32(sdO));
-        const uint64_t k_k0 = base_kmajor(smem_u32(sK)), v_k0 = base_kmajor(smem_u32(sV));
-        const uint64_t k_mn0 = base_mnmajor(smem_u32(sK));
-        bool ok = mbar_wait_w(qdo_full, 0, abort_flag);
-        ok = ok && mbar_wait_w(&k_full[0], 0, abort_flag);
-        ok = ok && mbar_wait_w(&v_full[0], 0, abort_flag);
+      // MMA warp of the "early" products: S(n+1) = Q K(n+1)^T as soon as the compute warps hold S(n) in
+      // registers, dP(n+1) = dO V(n+1)^T into the dP buffer that dQ(n-1) has released. A tcgen05.mma leaves
+      // its issuing thread only when the tensor core has room for it, so these must not queue behind dQ(n)
+      // in one warp's instruction stream: dQ has a warp of its own (below). dP lives in two TMEM buffers
+      // used alternately; with that the compute warps never wait for a tensor result of their own item.
+      constexpr uint32_t idesc_kk = make_idesc(BT, BT, 1, 1, 0, 0);
+      const uint32_t t_s = tmem_base, t_dp = tmem_base + 128;
+      const uint64_t q_addr = base_kmajor(smem_u32(sQ)), do_addr = base_kmajor(smem_u32(sdO));
+      const uint64_t k_k0 = base_kmajor(smem_u32(sK)), v_k0 = base_kmajor(smem_u32(sV));
+      bool ok = mbar_wait_w(qdo_full, 0, abort_flag);
+      ok = ok && mbar_wait_w(&k_full[0], 0, abort_flag);
+      ok = ok && mbar_wait_w(&v_full[0], 0, abort_flag);
+      tc_fence_after();
+      if (ok) {
+        umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, q_addr, k_k0, idesc_kk, 0u);
+        umma_commit_w(s_full);
+        umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, do_addr, v_k0, idesc_kk, 0u);
+        umma_commit_w(dp_full);
+        umma_commit_w(&v_empty[0]);
+      }
+      int n = 0;
+      for (; n + 1 < n_items && ok; ++n) {
+        const int ksn = (n + 1) % K_STAGES, vsn = (n + 1) % V_STAGES;
+        const uint64_t kn_addr = desc_advance(k_k0, (uint32_t)ksn * TILE_BYTES);
+        const uint64_t vn_addr = desc_advance(v_k0, (uint32_t)vsn * TILE_BYTES);
+        if (!mbar_wait_w(s_read, n & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_w(&k_full[ksn], ((n + 1) / K_STAGES) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        if (ok) {
-          umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, q_addr, k_k0, idesc_kk, 0u);
-          umma_commit_w(s_full);
-          umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, do_addr, v_k0, idesc_kk, 0u);
-          umma_commit_w(dp_full);
-          umma_commit_w(&v_empty[0]);
+        umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, q_addr, kn_addr, idesc_kk, 0u);
+        umma_commit_w(s_full);
+        // buffer (n+1) & 1 held dS(n-1), which dQ(n-1) reads
+        if (n >= 1 && !mbar_wait_w(&dp_free[(n + 1) & 1], ((n - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_w(&v_full[vsn], ((n + 1) / V_STAGES) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp + (uint32_t)((n + 1) & 1) * 256, do_addr, vn_addr, idesc_kk, 0u);
+        umma_commit_w(dp_full);
+        umma_commit_w(&v_empty[vsn]);   // V(n+1) is only read by dP(n+1)
+      }
+      if (!ok) {
+        if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
+        umma_commit_w(&drain_bar[0]);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&drain_bar[0], 0) && globaltimer_ns() - t0 < 50000000ull) {
         }
-        int n = 0;
-        for (; n < n_items && ok; ++n) {
-          const int ks = n % K_STAGES, ksn = (n + 1) % K_STAGES, vsn = (n + 1) % V_STAGES;
-          const bool has_next = n + 1 < n_items;
-          const uint64_t k_addr = desc_advance(k_mn0, (uint32_t)ks * TILE_BYTES);   // read transposed
-          const uint64_t kn_addr = desc_advance(k_k0, (uint32_t)ksn * TILE_BYTES);
-          const uint64_t vn_addr = desc_advance(v_k0, (uint32_t)vsn * TILE_BYTES);
-          if (has_next) {
-            if (!mbar_wait_w(s_read, n & 1, abort_flag)) { ok = false; break; }
-            if (!mbar_wait_w(&k_full[ksn], ((n + 1) / K_STAGES) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_s, q_addr, kn_addr, idesc_kk, 0u);
-            umma_commit_w(s_full);
-          }
-          if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          if (lane == 0) ZX_TRACE(n, 8);
-          umma_ts_k8_w<8, 16, 24, 64, 72, 80, 88>(t_dq, t_dp, k_addr, idesc_tm, n > 0 ? 1u : 0u);
-          umma_commit_w(&k_empty[ks]);    // K(n) has now served S(n) and dQ(n)
-          if (lane == 0) ZX_TRACE(n, 9);
-          if (has_next) {
-            if (!mbar_wait_w(&v_full[vsn], ((n + 1) / V_STAGES) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            umma_ss_k8_kmajor_w<HALF_BYTES / 16>(t_dp, do_addr, vn_addr, idesc_kk, 0u);
-            umma_commit_w(dp_full);
-            umma_commit_w(&v_empty[vsn]);   // V(n+1) is only read by dP(n+1)
-          }
-          if (lane == 0) ZX_TRACE(n, 10);
-        }
-        if (ok) umma_commit_w(acc_done);
-        if (!ok) {
-          if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
-          umma_commit_w(drain_bar);
-          const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 50000000ull) {
-          }
+      }
+    } else if (warp == W_MMA_DQ) {
+      // MMA warp of dQ(n) += dS(n) K(n): A = dS from the dP buffer of item n, B = K(n) read transposed
+      constexpr uint32_t idesc_tm = make_idesc(BT, HD, 1, 1, 0, 1);
+      const uint32_t t_dp = tmem_base + 128, t_dq = tmem_base + 256;
+      const uint64_t k_mn0 = base_mnmajor(smem_u32(sK));
+      bool ok = true;
+      int n = 0;
+      for (; n < n_items && ok; ++n) {
+        const int ks = n % K_STAGES;
+        if (!mbar_wait_w(ds_ready, n & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) ZX_TRACE(n, 8);
+        umma_ts_k8_w<8, 16, 24, 64, 72, 80, 88>(t_dq, t_dp + (uint32_t)(n & 1) * 256,
+                                                 desc_advance(k_mn0, (uint32_t)ks * TILE_BYTES), idesc_tm, n > 0 ? 1u : 0u);
+        umma_commit_w(&k_empty[ks]);        // K(n) has now served S(n) and dQ(n)
+        umma_commit_w(&dp_free[n & 1]);
+        if (lane == 0) ZX_TRACE(n, 9);
+      }
+      if (ok) umma_commit_w(acc_done);
+      if (!ok) {
+        if (lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/22, n);
+        umma_commit_w(&drain_bar[1]);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&drain_bar[1], 0) && globaltimer_ns() - t0 < 50000000ull) {
         }
       }
     } else {
@@ -727,7 +746,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int r = lq * 32 + lane;  // query row == TMEM lane
       const int col0 = wg * 64;
       const uint32_t lane_base = (uint32_t)(lq * 32) << 16;
-      const uint32_t t_s = tmem_base + lane_base + col0, t_dp = tmem_base + lane_base + 128 + col0;
+      const uint32_t t_s = tmem_base + lane_base + col0, t_dp0 = tmem_base + lane_base + 128 + col0;
       const size_t stat_idx = ((size_t)b * p.Hq + hq) * p.Sq + (size_t)t * BT + r;
       const float lse2 = p.lse[stat_idx] * LOG2E;
       const float dlt = p.delta[stat_idx];
@@ -769,6 +788,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!wait_warp(dp_full, n & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (threadIdx.x == 0) ZX_TRACE(n, 3);
+        const uint32_t t_dp = t_dp0 + (n & 1) * 256;   // the two dP buffers sit at columns 128 and 384
         uint32_t dp[64];
         tmem_ld_32x32b_x32(t_dp + 0, dp);
         tmem_ld_32x32b_x32(t_dp + 32, dp + 32);
