@@ -19,6 +19,86 @@ import torch
 import torch.distributed as dist
 
 
+def slice_check(ring, q, k, v, do, o, lse, dq, dk, dv, scale, mask, n_check=16384):
+    """fp32 reference on two slices of the global sequence, computed on every rank from all-reduced copies:
+
+    * the FIRST ``n_check`` positions: O, LSE and dQ of those queries only involve keys of the same slice;
+    * the LAST ``n_check`` positions: dK and dV of those keys only receive from queries of the same slice
+      (their softmax runs over the whole sequence, so the reference takes the kernels' LSE and
+      delta = rowsum(dO * O) for those rows, which the first slice has verified in kind).
+
+    Returns relative Frobenius errors and maximum absolute errors per tensor."""
+    R, S = ring.degree, ring.seq_len
+    dev = q.device
+    Lc = q.shape[1] // len(ring.positions())
+
+    def collect(x, lo, hi, token_dim=1):
+        """[.., hi - lo tokens, ..] in global order: each rank places the tokens it owns, the rest are zeros."""
+        shape = list(x.shape)
+        shape[token_dim] = hi - lo
+        out = torch.zeros(shape, device=dev, dtype=torch.float32)
+        for ci, p0 in enumerate(ring.positions()):
+            a, b = max(p0, lo), min(p0 + Lc, hi)
+            if a < b:
+                src = x.narrow(token_dim, ci * Lc + (a - p0), b - a).float()
+                out.narrow(token_dim, a - lo, b - a).copy_(src)
+        if R > 1:
+            dist.all_reduce(out)
+        return out
+
+    def masked_scores(qs, ks, q0, k0):
+        qpos = torch.arange(q0, q0 + qs.shape[1], device=dev)
+        kpos = torch.arange(k0, k0 + ks.shape[1], device=dev)
+        keep = kpos[None, :] <= qpos[:, None]
+        if mask.window_blocks > 0:
+            qb, kb = qpos[:, None] // 128, kpos[None, :] // 128
+            win = (qb - kb).abs() < mask.window_blocks
+            glob = (kb % mask.global_every == 0) if mask.global_every > 0 else torch.zeros_like(win)
+            keep = keep & (win | glob)
+        return keep
+
+    def err(a, b):
+        return {"rel": round(float((a - b).norm() / (b.norm() + 1e-20)), 5), "max_abs": round(float((a - b).abs().max()), 5)}
+
+    G = q.shape[2] // k.shape[2]
+    res = {"slice_tokens": n_check}
+    # ---- first slice: O, LSE, dQ
+    qf, dof = collect(q, 0, n_check), collect(do, 0, n_check)
+    kf, vf = collect(k, 0, n_check), collect(v, 0, n_check)
+    of, dqf = collect(o, 0, n_check), collect(dq, 0, n_check)
+    lsef = collect(lse, 0, n_check, token_dim=2)
+    keep = masked_scores(qf, kf, 0, 0)
+    o_ref, dq_ref, lse_ref = torch.empty_like(of), torch.empty_like(dqf), torch.empty_like(lsef)
+    for h in range(q.shape[2]):
+        s = (qf[0, :, h] @ kf[0, :, h // G].T) * scale
+        s = s.masked_fill(~keep, float("-inf"))
+        lse_h = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - lse_h[:, None])
+        oh = p @ vf[0, :, h // G]
+        dp = dof[0, :, h] @ vf[0, :, h // G].T
+        ds = p * (dp - (dof[0, :, h] * oh).sum(-1, keepdim=True))
+        o_ref[0, :, h], lse_ref[0, h], dq_ref[0, :, h] = oh, lse_h, (ds @ kf[0, :, h // G]) * scale
+    res["o"], res["lse"], res["dq"] = err(of, o_ref), err(lsef, lse_ref), err(dqf, dq_ref)
+    # ---- last slice: dK, dV
+    lo = S - n_check
+    ql, dol, ol = collect(q, lo, S), collect(do, lo, S), collect(o, lo, S)
+    kl, vl = collect(k, lo, S), collect(v, lo, S)
+    dkl, dvl = collect(dk, lo, S), collect(dv, lo, S)
+    lsel = collect(lse, lo, S, token_dim=2)
+    keep = masked_scores(ql, kl, lo, lo)
+    dk_ref, dv_ref = torch.zeros_like(dkl), torch.zeros_like(dvl)
+    for h in range(q.shape[2]):
+        s = (ql[0, :, h] @ kl[0, :, h // G].T) * scale
+        p = torch.exp(s - lsel[0, h][:, None]).masked_fill(~keep, 0.0)
+        dp = dol[0, :, h] @ vl[0, :, h // G].T
+        ds = p * (dp - (dol[0, :, h] * ol[0, :, h]).sum(-1, keepdim=True))
+        dv_ref[0, :, h // G] += p.T @ dol[0, :, h]
+        dk_ref[0, :, h // G] += (ds.T @ ql[0, :, h]) * scale
+    res["dk"], res["dv"] = err(dkl, dk_ref), err(dvl, dv_ref)
+    res["ok"] = all(res[n]["rel"] < 2e-2 for n in ("o", "dq", "dk", "dv")) and res["lse"]["max_abs"] < 2e-2
+    return res
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--seq-len", type=int, default=131072)
@@ -101,8 +181,12 @@ def main(argv=None):
            "per_gpu_tflops": round((f_fwd + f_bwd) / (ms_f + ms_b) / 1e9 / R, 1),
            "roofline_ms": round(roof_s * 1e3, 2), "frac_of_roofline": round(roof_s * 1e3 / (ms_f + ms_b), 3),
            "peaks": pk["source"], "timing": "CUDA events, max over ranks, median of %d" % args.iters}
-    if args.check and r == 0:
-        rec["check"] = "see tests/test_gpu_dist.py (ring vs single-GPU) and tests/test_gpu_kernels.py (vs fp32)"
+    if args.check:
+        dq, dk, dv = ring_attn_backward(ring, q, k, v, o, do, lse, scale, 0)
+        chk = slice_check(ring, q, k, v, do, o, lse, dq, dk, dv, scale, mask, n_check=min(16384, S // 2))
+        _ext.check_status()
+        if r == 0:
+            rec["check"] = chk
     if r == 0:
         print(json.dumps(rec), flush=True)
     if peer is not None:
