@@ -518,7 +518,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // column group drains its 32 columns of both accumulators
       if (ok) ok = wait_warp(acc_done, 0, abort_flag);
       tc_fence_after();
-      if (ok) {
+      if (ok && ZX_IN_BOUNDS(p.status, j * BT + r, p.Skv, 24)) {
         const size_t row_off = (((size_t)b * p.Skv + (size_t)j * BT + r) * p.Hkv + hk) * HD + col0;
         float* dv_row = p.dv + row_off;
         float* dk_row = p.dk + row_off;
@@ -815,7 +815,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (ok) ok = wait_warp(acc_done, 0, abort_flag);
       tc_fence_after();
-      if (ok) {
+      if (ok && ZX_IN_BOUNDS(p.status, t * BT + r, p.Sq, 25)) {
         float* dq_row = p.dq + (((size_t)b * p.Sq + (size_t)t * BT + r) * p.Hq + hq) * HD + col0;
 #pragma unroll
         for (int ci = 0; ci < 2; ++ci) {

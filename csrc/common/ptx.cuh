@@ -19,6 +19,17 @@ __device__ __forceinline__ void report(Status* st, int code, int site, int info)
   }
 }
 
+// Checked build (-DZX_CHECKED, `python -m zenyx_b200._build --checked`): the index of every global-memory row a
+// kernel epilogue writes is compared with its extent first; a bad index is recorded in the status word
+// (ZX_ERR_BOUNDS with the site and the index) and the access is skipped, so the context stays usable and the
+// host reads what went wrong. In normal builds the macro is the constant `true` and costs nothing.
+#ifdef ZX_CHECKED
+#define ZX_IN_BOUNDS(st, idx, limit, site) \
+  ((unsigned long long)(idx) < (unsigned long long)(limit) ? true : (::zx::report((st), ::zx::ZX_ERR_BOUNDS, (site), (int)(idx)), false))
+#else
+#define ZX_IN_BOUNDS(st, idx, limit, site) true
+#endif
+
 // ----------------------------------------------------------------------------------------------
 // Basic helpers
 // ----------------------------------------------------------------------------------------------

@@ -252,6 +252,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (p.scatter_ranks > 0) {
               // reduce-scatter fused into the epilogue: this partial row goes to the slot its owner keeps for us
               const int owner = row / p.scatter_rows_per_rank;
+              if (!ZX_IN_BOUNDS(p.status, owner, p.scatter_ranks, 4)) continue;
               crow = p.scatter_base[owner] +
                      ((size_t)p.scatter_src_rank * p.scatter_rows_per_rank + (row - owner * p.scatter_rows_per_rank)) * p.ldc;
             }

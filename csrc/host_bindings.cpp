@@ -5,6 +5,7 @@
 #include <pybind11/stl.h>
 
 #include "cpu_ref/flash_cpu.h"
+#include "cpu_ref/quant_adamw_ref.h"
 #include "attn/tile_iter_host.h"
 #include "peer/barrier_model.h"
 #include "tier/belady_min.h"
@@ -45,6 +46,31 @@ CpuAttnShape shape_of(const FArr& q, const FArr& k, float scale, bool causal, in
 }  // namespace
 
 PYBIND11_MODULE(_host, m) {
+  m.def("quant_e4m3_ref", [](py::array_t<float, py::array::c_style | py::array::forcecast> x, int block_tokens) {
+    if (x.ndim() != 3) throw std::runtime_error("quant_e4m3_ref: x must be [tokens, heads, dim]");
+    const int64_t tokens = x.shape(0);
+    const int heads = (int)x.shape(1), dim = (int)x.shape(2);
+    py::array_t<uint8_t> q({(py::ssize_t)tokens, (py::ssize_t)heads, (py::ssize_t)dim});
+    py::array_t<float> sc({(py::ssize_t)((tokens + block_tokens - 1) / block_tokens), (py::ssize_t)heads});
+    zx::quant_e4m3_ref(x.data(), q.mutable_data(), sc.mutable_data(), tokens, heads, dim, block_tokens);
+    return py::make_tuple(q, sc);
+  }, py::arg("x"), py::arg("block_tokens") = 128);
+  m.def("e4m3_to_float", [](py::array_t<uint8_t, py::array::c_style | py::array::forcecast> q) {
+    py::array_t<float> out(q.size());
+    for (py::ssize_t i = 0; i < q.size(); ++i) out.mutable_data()[i] = zx::e4m3_to_float(q.data()[i]);
+    return out;
+  });
+  m.def("adamw_split_master_ref", [](py::array_t<uint16_t, py::array::c_style> p_hi, py::array_t<int16_t, py::array::c_style> p_lo,
+                                     py::array_t<float, py::array::c_style> mm, py::array_t<float, py::array::c_style> vv,
+                                     py::array_t<float, py::array::c_style | py::array::forcecast> g, size_t decay_end, float lr,
+                                     float beta1, float beta2, float eps, float weight_decay, int step) {
+    const size_t n = (size_t)p_hi.size();
+    if ((size_t)p_lo.size() != n || (size_t)mm.size() != n || (size_t)vv.size() != n || (size_t)g.size() != n)
+      throw std::runtime_error("adamw_split_master_ref: size mismatch");
+    zx::adamw_split_master_ref(p_hi.mutable_data(), p_lo.mutable_data(), mm.mutable_data(), vv.mutable_data(), g.data(), n,
+                               decay_end, lr, beta1, beta2, eps, weight_decay, step);
+  }, "in place on p_hi (bf16 bits), p_lo, m, v");
+
   m.def("tile_iter_mismatches", &zx::tile_iter_mismatches, py::arg("causal"), py::arg("window_blocks"),
         py::arg("global_every"), py::arg("q_chunk_pos"), py::arg("kv_chunk_pos"), py::arg("q_tiles_per_chunk"),
         py::arg("kv_tiles_per_chunk"));

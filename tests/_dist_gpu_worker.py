@@ -53,6 +53,11 @@ def case_ring(ctx):
             "dv": rel(dv, shard_sequence(dv_ref, r, R)),
         }
         assert all(e < 2e-2 for e in errs.values()), (mask, errs)
+        # the ring result against fp32 math as well (not only against this package's single-GPU kernels)
+        from zenyx_b200.bench.ring_attn import slice_check
+
+        chk = slice_check(ring, ql, ks, vs, dol, o, lse, dq, dk, dv, scale, mask, n_check=S // 2)
+        assert chk["ok"] and max(chk[n]["max_abs"] for n in ("o", "dq", "dk", "dv")) < 0.25, chk
         torch.cuda.synchronize()
         dist.barrier()
         peer.close()

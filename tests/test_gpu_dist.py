@@ -36,3 +36,10 @@ def test_two_gpus(case):
 def test_four_gpus(case):
     out = _run(case, 4)
     assert f"{case} ok" in out
+
+
+@pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("case", ["ring", "zero", "train", "tp"])
+def test_eight_gpus(case):
+    out = _run(case, 8)
+    assert f"{case} ok" in out

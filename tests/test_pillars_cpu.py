@@ -275,3 +275,34 @@ def test_fused_collective_path_choice_follows_the_measurements():
     assert _pull_hides_under_gemm(16384, 4096, 14336)        # 2 GPUs, gate|up: fused measured 1.19x
     assert _pull_hides_under_gemm(4096, 4096, 3584)          # 8 GPUs with the 16-deep pull: 56 us copy, 92 us math
     assert not _pull_hides_under_gemm(4096, 4096, 512)       # a narrow projection cannot hide its operand's copy
+
+
+def test_cpp_quantiser_and_adamw_oracles_agree_with_the_python_paths():
+    """csrc/cpu_ref/quant_adamw_ref.cpp restates the e4m3 K/V quantiser and one AdamW step on the split master
+    in scalar C++; the torch CPU paths (which the GPU tests compare the kernels with) must agree with it."""
+    host = _ext.host()
+    torch.manual_seed(11)
+    # --- quantiser: same codes and scales, including values at and beyond the format's edges
+    x = torch.randn(300, 2, 128) * torch.logspace(-3, 2, 300)[:, None, None]
+    x[0, 0, :8] = torch.tensor([0.0, -0.0, 1e-9, 448.0, -448.0, 1e6, 2.0 ** -9, 3 * 2.0 ** -10])
+    q_ref, s_ref = host.quant_e4m3_ref(x.numpy(), 128)
+    q, s = fused.kv_quantize_e4m3(x, 128)
+    assert np.allclose(s.numpy(), s_ref, rtol=1e-6)
+    a, b = host.e4m3_to_float(q.view(torch.uint8).numpy()).reshape(x.shape), host.e4m3_to_float(q_ref).reshape(x.shape)
+    assert np.array_equal(a, b)                       # same value for every element (+0 and -0 compare equal)
+    deq = fused.kv_dequantize_e4m3(q, s, 128, dtype=torch.float32)
+    assert float(((deq - x).abs() / (s[torch.arange(300) // 128][:, :, None] * 448)).max()) <= 2.0 ** -4   # half a step at the top binade
+    # --- AdamW on the split master, three steps
+    n = 4096
+    w = torch.randn(n) * 0.02
+    hi, lo = fused.split_master(w)
+    m, v = torch.zeros(n), torch.zeros(n)
+    hi_r, lo_r = hi.clone().view(torch.int16).numpy().view(np.uint16).copy(), lo.clone().numpy().copy()
+    m_r, v_r = m.numpy().copy(), v.numpy().copy()
+    for step in (1, 2, 3):
+        g = torch.randn(n) * 1e-2
+        fused.adamw_step_(hi, lo, m, v, g, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+        host.adamw_split_master_ref(hi_r, lo_r, m_r, v_r, g.numpy(), n, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
+    w_py = fused.join_master(hi, lo)
+    w_cc = fused.join_master(torch.from_numpy(hi_r.view(np.int16)).view(torch.bfloat16), torch.from_numpy(lo_r))
+    assert torch.allclose(w_py, w_cc, rtol=0, atol=2e-7) and np.allclose(m.numpy(), m_r, atol=1e-9) and np.allclose(v.numpy(), v_r, atol=1e-12)

@@ -36,7 +36,7 @@ CUDA_SOURCES = [
     "noalloc/attn_bwd_static.cu",
 ]
 CUDA_CPP_SOURCES = ["bindings.cpp", "peer/ipc_memory.cpp"]
-HOST_SOURCES = ["tier/belady_min.cpp", "tier/tier_engine.cpp", "cpu_ref/flash_cpu.cpp", "peer/barrier_model.cpp", "attn/tile_iter_host.cpp",
+HOST_SOURCES = ["tier/belady_min.cpp", "tier/tier_engine.cpp", "cpu_ref/flash_cpu.cpp", "cpu_ref/quant_adamw_ref.cpp", "peer/barrier_model.cpp", "attn/tile_iter_host.cpp",
                 "host_bindings.cpp"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -97,27 +97,32 @@ def existing(sources):
     return [s for s in sources if (CSRC / s).exists()]
 
 
-def build_cuda_extension(verbose: bool = False) -> Path:
-    """Compile every CUDA kernel for sm_100a and link ``zenyx_b200/_C.so``."""
+def build_cuda_extension(verbose: bool = False, checked: bool = False) -> Path:
+    """Compile every CUDA kernel for sm_100a and link ``zenyx_b200/_C.so``. ``checked=True`` builds the same
+    sources with ``-DZX_CHECKED`` (in-kernel index checks that record a bad index in the status word and skip the
+    access) into ``zenyx_b200/_checked/_C.so``; load it with ``ZENYX_B200_EXT_DIR=<repo>/zenyx_b200/_checked``."""
     inc, defs, libdirs, cuda_home = _torch_flags()
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    obj_dir = CSRC / ("_obj_checked" if checked else "_obj")
+    obj_dir.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
     nvcc_prefix = [nvcc, *ARCH_FLAGS, "-std=c++17", "-O3", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC",
-                   f"-I{CSRC}"]
+                   f"-I{CSRC}"] + (["-DZX_CHECKED"] if checked else [])
     cxx_prefix = ["g++", "-std=c++17", "-O2", "-fPIC", "-DTORCH_EXTENSION_NAME=_C", f"-I{CSRC}", *inc, *defs]
     jobs = []
     objs = []
     for s in existing(CUDA_SOURCES):
-        obj = OBJ_DIR / (s.replace("/", "_") + ".o")
+        obj = obj_dir / (s.replace("/", "_") + ".o")
         objs.append(obj)
         jobs.append((CSRC / s, obj, nvcc_prefix, "".join(nvcc_prefix)))
     for s in existing(CUDA_CPP_SOURCES):
-        obj = OBJ_DIR / (s.replace("/", "_") + ".o")
+        obj = obj_dir / (s.replace("/", "_") + ".o")
         objs.append(obj)
         jobs.append((CSRC / s, obj, cxx_prefix, "".join(cxx_prefix)))
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
         changed = list(ex.map(lambda j: _compile_one(j[0], j[1], j[2], verbose, j[3]), jobs))
-    out = PKG_DIR / "_C.so"
+    out_dir = PKG_DIR / "_checked" if checked else PKG_DIR
+    out_dir.mkdir(exist_ok=True)
+    out = out_dir / "_C.so"
     if any(changed) or not out.exists():
         link = ["g++", "-shared", "-o", str(out), *map(str, objs)]
         for d in libdirs:
@@ -148,13 +153,18 @@ def build_host_extension(verbose: bool = False) -> Path:
     return out
 
 
-def build_all(verbose: bool = False):
+def build_all(verbose: bool = False, checked: bool = False):
     outs = [build_host_extension(verbose)]
     if Path(_nvcc()).exists():
         outs.append(build_cuda_extension(verbose))
+        if checked:
+            import shutil
+
+            outs.append(build_cuda_extension(verbose, checked=True))
+            shutil.copy2(PKG_DIR / "_host.so", PKG_DIR / "_checked" / "_host.so")
     return outs
 
 
 if __name__ == "__main__":
-    for o in build_all(verbose="-v" in sys.argv):
+    for o in build_all(verbose="-v" in sys.argv, checked="--checked" in sys.argv):
         print("built", o)

@@ -101,6 +101,8 @@ _SITES = {
     11: "attn_fwd: TMA producer", 12: "attn_fwd: MMA issuer", 13: "attn_fwd: softmax",
     21: "attn_bwd: TMA producer", 22: "attn_bwd: MMA issuer", 23: "attn_bwd: compute warps",
     31: "peer barrier", 41: "zero_adamw: peer flag",
+    4: "gemm: reduce-scatter owner index", 14: "attn_fwd: output row", 15: "attn_fwd: batch index",
+    24: "attn_bwd: dK/dV row", 25: "attn_bwd: dQ row",
 }
 
 
