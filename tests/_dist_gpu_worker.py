@@ -61,6 +61,33 @@ def case_ring(ctx):
         torch.cuda.synchronize()
         dist.barrier()
         peer.close()
+    # e4m3 cache format in the peer slots and on the wire: same result as one GPU attending the round-tripped K/V
+    from zenyx_b200.train.fp8_kv_quantization import FP8KVQuantizer
+
+    qz = FP8KVQuantizer(Hkv, D, 128)
+    kq, vq = qz.roundtrip(k), qz.roundtrip(v)
+    mask = MaskSpec(True)
+    o_ref = torch.empty_like(q)
+    lse_ref = torch.empty(B, Hq, S, device="cuda")
+    attn_forward(q, kq, vq, o_ref, lse_ref, scale, mask, [0], [0])
+    dq_ref = torch.empty(B, S, Hq, D, device="cuda")
+    dk_ref = torch.zeros(B, S, Hkv, D, device="cuda")
+    dv_ref = torch.zeros(B, S, Hkv, D, device="cuda")
+    attn_backward(q, kq, vq, o_ref, do, lse_ref, torch.empty_like(lse_ref), dq_ref, dk_ref, dv_ref, scale, mask, [0], [0])
+    peer = RingBuffers((B, S // R, Hkv, D), group=None, timeout_ms=5000.0, fp8_block_tokens=128)
+    ring = RingContext(rank=r, degree=R, seq_len=S, peer=peer, mask=mask)
+    ql, dol = shard_sequence(q, r, R).contiguous(), shard_sequence(do, r, R).contiguous()
+    kl, vl = shard_sequence(k, r, R).contiguous(), shard_sequence(v, r, R).contiguous()
+    o, lse = ring_attn_forward(ring, ql, kl, vl, scale, 0)
+    dq, dk, dv = ring_attn_backward(ring, ql, kl, vl, o, dol, lse, scale, 0)
+    _ext.check_status()
+    errs = {"o": rel(o, shard_sequence(o_ref, r, R)), "dq": rel(dq, shard_sequence(dq_ref, r, R)),
+            "dk": rel(dk, shard_sequence(dk_ref, r, R)), "dv": rel(dv, shard_sequence(dv_ref, r, R))}
+    assert all(e < 2e-2 for e in errs.values()), ("fp8 ring", errs)
+    assert peer.pull_args((r + 1) % R, 0, 0)[2] < 0.55 * 2 * (S // R) * Hkv * D * 2    # about half the bf16 bytes
+    torch.cuda.synchronize()
+    dist.barrier()
+    peer.close()
     print(f"rank {r}: ring ok", flush=True)
 
 

@@ -107,6 +107,8 @@ def main(argv=None):
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--window-tokens", type=int, default=0, help="> 0: block-sparse (window + --global-every)")
     ap.add_argument("--global-every", type=int, default=64)
+    ap.add_argument("--fp8-kv", action="store_true",
+                    help="K/V in the e4m3 cache format (per head and 128-token block scales): codes in the peer slots and on NVLink")
     args = ap.parse_args(argv)
 
     from zenyx_b200.bench.kernels import peaks
@@ -127,13 +129,22 @@ def main(argv=None):
     if R > 1:
         from zenyx_b200.parallel.peer import RingBuffers
 
-        peer = RingBuffers((B, Sl, Hkv, D), group=None)
-        k, v = peer.kv_views(r, 0)
-        k.copy_(torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16())
-        v.copy_(torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16())
+        peer = RingBuffers((B, Sl, Hkv, D), group=None, fp8_block_tokens=128 if args.fp8_kv else 0)
+        if args.fp8_kv:
+            k = torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16()
+            v = torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16()
+        else:
+            k, v = peer.kv_views(r, 0)
+            k.copy_(torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16())
+            v.copy_(torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16())
     else:
         k = torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16()
         v = torch.randn(B, Sl, Hkv, D, device=dev, generator=g).bfloat16()
+        if args.fp8_kv:   # one GPU: no slots, the cache format is a round trip
+            from zenyx_b200.train.fp8_kv_quantization import FP8KVQuantizer
+
+            qz = FP8KVQuantizer(Hkv, D, 128)
+            k, v = qz.roundtrip(k), qz.roundtrip(v)
     ring = RingContext(rank=r, degree=R, seq_len=S, peer=peer, mask=mask)
 
     def sync():
@@ -170,11 +181,12 @@ def main(argv=None):
     f_fwd = 4.0 * S * S * D * Hq * 0.5 * density
     f_bwd = 2.5 * f_fwd
     pk = peaks()
-    kv_bytes = 2 * Sl * Hkv * D * 2
-    nvlink_s = (2 * kv_bytes + 2 * kv_bytes * 2) * (R - 1) / 770e9            # fwd pull + bwd pull + fp32 dK/dV push
+    kv_bytes = 2 * Sl * Hkv * D * (1 if args.fp8_kv else 2)                   # K and V of one rank as they travel
+    nvlink_s = (2 * kv_bytes + 2 * Sl * Hkv * D * 4) * (R - 1) / 770e9        # fwd pull + bwd pull + fp32 dK/dV push
     roof_s = max((f_fwd + f_bwd) / R / (pk["tflops_sustained"] * 1e12), nvlink_s)
     rec = {"metric": "ring-attn fwd+bwd TFLOP/s", "ring_degree": R, "seq_len": S, "heads": [Hq, Hkv], "head_dim": D,
-           "layout": "zigzag", "mask": "causal" + (f"+window{args.window_tokens}+global{args.global_every}" if args.window_tokens else ""),
+           "layout": "zigzag", "kv_format": "e4m3 + fp32 scale per (head, 128 tokens)" if args.fp8_kv else "bf16",
+           "mask": "causal" + (f"+window{args.window_tokens}+global{args.global_every}" if args.window_tokens else ""),
            "fwd_ms": round(ms_f, 3), "bwd_ms": round(ms_b, 3),
            "fwd_tflops": round(f_fwd / ms_f / 1e9, 1), "bwd_tflops": round(f_bwd / ms_b / 1e9, 1),
            "value": round((f_fwd + f_bwd) / (ms_f + ms_b) / 1e9, 1), "unit": "TFLOP/s (whole job)",
@@ -183,7 +195,13 @@ def main(argv=None):
            "peaks": pk["source"], "timing": "CUDA events, max over ranks, median of %d" % args.iters}
     if args.check:
         dq, dk, dv = ring_attn_backward(ring, q, k, v, o, do, lse, scale, 0)
-        chk = slice_check(ring, q, k, v, do, o, lse, dq, dk, dv, scale, mask, n_check=min(16384, S // 2))
+        k_ref, v_ref = k, v
+        if args.fp8_kv:   # the reference attends what the cache format holds
+            from zenyx_b200.train.fp8_kv_quantization import FP8KVQuantizer
+
+            qz = FP8KVQuantizer(Hkv, D, 128)
+            k_ref, v_ref = qz.roundtrip(k), qz.roundtrip(v)
+        chk = slice_check(ring, q, k_ref, v_ref, do, o, lse, dq, dk, dv, scale, mask, n_check=min(16384, S // 2))
         _ext.check_status()
         if r == 0:
             rec["check"] = chk

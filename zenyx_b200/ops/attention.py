@@ -325,16 +325,24 @@ def ring_attn_forward(ctx: RingContext, q, k, v, scale: float, slot: int = 0):
             lse.fill_(float("-inf"))
         return o, lse
     peer = ctx.peer
+    fp8 = getattr(peer, "fp8_block_tokens", 0) > 0
+    if fp8:   # e4m3 cache: this rank's K/V go into its slot as codes + scales; peers pull those (half the bytes)
+        peer.quantize_into_slot(k, v, slot)
     peer.barrier()  # every rank's K/V slot is written and visible
     for i, s in enumerate(steps):
         owner = ctx.owner_at(s)
-        kk, vv = (k, v) if owner == ctx.rank else peer.staged_kv(i % 2, k.shape)
+        if fp8:   # every step works on what the cache format can represent, the local one included
+            kk, vv = peer.dequant_local(slot) if owner == ctx.rank else (None, None)
+        else:
+            kk, vv = (k, v) if owner == ctx.rank else peer.staged_kv(i % 2, k.shape)
         pull = None
         if i + 1 < len(steps):
             nxt = ctx.owner_at(steps[i + 1])
             pull = peer.pull_args(nxt, slot, (i + 1) % 2) if nxt != ctx.rank else None
         if i == 0 and owner != ctx.rank:
             peer.pull_now(owner, slot, 0)  # first active step is remote: nothing to overlap with yet
+        if fp8 and owner != ctx.rank:
+            kk, vv = peer.dequant_staged(i % 2)
         attn_forward(q, kk, vv, o, lse, scale, ctx.mask, ctx.positions(), ctx.positions(owner), i > 0, pull)
     if not steps:
         o.zero_()
@@ -371,17 +379,25 @@ def ring_attn_backward(ctx: RingContext, q, k, v, o, d_o, lse, scale: float, slo
         dist.all_reduce(dv_all, group=ctx.group)
         return dq, dk_all[ctx.rank], dv_all[ctx.rank]
     peer = ctx.peer
+    fp8 = getattr(peer, "fp8_block_tokens", 0) > 0
+    if fp8:   # the slot may have been reused since the forward: put this call's K/V back (same codes)
+        peer.quantize_into_slot(k, v, slot)
     peer.zero_dkv(slot)
     peer.barrier()  # accumulators cleared everywhere, K/V slots still valid
     for i, s in enumerate(steps):
         owner = ctx.owner_at(s)
-        kk, vv = (k, v) if owner == ctx.rank else peer.staged_kv(i % 2, k.shape)
+        if fp8:   # gradients are taken at the values the cache format holds (straight-through for K and V)
+            kk, vv = peer.dequant_local(slot) if owner == ctx.rank else (None, None)
+        else:
+            kk, vv = (k, v) if owner == ctx.rank else peer.staged_kv(i % 2, k.shape)
         pull = None
         if i + 1 < len(steps):
             nxt = ctx.owner_at(steps[i + 1])
             pull = peer.pull_args(nxt, slot, (i + 1) % 2) if nxt != ctx.rank else None
         if i == 0 and owner != ctx.rank:
             peer.pull_now(owner, slot, 0)
+        if fp8 and owner != ctx.rank:
+            kk, vv = peer.dequant_staged(i % 2)
         dk_t, dv_t = peer.dkv_views(owner, slot, k.shape)
         attn_backward(q, kk, vv, o, d_o, lse, delta, dq, dk_t, dv_t, scale, ctx.mask, ctx.positions(),
                       ctx.positions(owner), i == 0, i > 0, pull)
@@ -395,14 +411,14 @@ def ring_attn_backward(ctx: RingContext, q, k, v, o, d_o, lse, scale: float, slo
 class _RingAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale, ring):
-        if ring.degree > 1 and q.is_cuda:
+        slots = ring.degree > 1 and q.is_cuda and getattr(ring.peer, "fp8_block_tokens", 0) == 0
+        if slots:   # bf16 ring: K/V live in this rank's peer-visible slot (the e4m3 ring quantises into it itself)
             ks, vs = ring.peer.kv_views(ring.rank, 0, k.shape)
             ks.copy_(k)
             vs.copy_(v)
             k, v = ks, vs
         o, lse = ring_attn_forward(ring, q, k, v, scale, 0)
-        ctx.save_for_backward(q, k.clone() if (ring.degree > 1 and q.is_cuda) else k,
-                              v.clone() if (ring.degree > 1 and q.is_cuda) else v, o, lse)
+        ctx.save_for_backward(q, k.clone() if slots else k, v.clone() if slots else v, o, lse)
         ctx.cfg = (scale, ring)
         return o
 
@@ -410,7 +426,7 @@ class _RingAttnFn(torch.autograd.Function):
     def backward(ctx, d_o):
         q, k, v, o, lse = ctx.saved_tensors
         scale, ring = ctx.cfg
-        if ring.degree > 1 and q.is_cuda:
+        if ring.degree > 1 and q.is_cuda and getattr(ring.peer, "fp8_block_tokens", 0) == 0:
             ks, vs = ring.peer.kv_views(ring.rank, 0, k.shape)
             ks.copy_(k)
             vs.copy_(v)
@@ -427,8 +443,10 @@ def ring_flash_attention(q, k, v, *, causal: bool = True, scale: Optional[float]
     q [B,S_local,Hq,128], k/v [B,S_local,Hkv,128] hold the tokens given by
     ``shard_positions(rank, degree, seq_len, layout)``. Pass a prepared ``RingContext`` (GPU ranks
     need its peer buffers), or a process ``group`` for the CPU/gloo fallback. ``kv_fp8`` is an
-    optional ``FP8KVQuantizer``: K/V then take a round trip through e4m3 with per-(head, block)
-    scales before use, i.e. the op computes attention over the quantised cache.
+    optional ``FP8KVQuantizer``: the op then computes attention over the e4m3 cache (per-(head, block)
+    scales). On GPU ranks whose ``RingContext.peer`` was built with ``fp8_block_tokens`` the codes and
+    scales are what sits in the peer slots and crosses NVLink; otherwise K/V take a round trip through
+    the format before the bf16 ring.
     """
     import torch.distributed as dist
 
@@ -438,6 +456,7 @@ def ring_flash_attention(q, k, v, *, causal: bool = True, scale: Optional[float]
         rank = dist.get_rank(group) if degree > 1 else 0
         ring = RingContext(rank=rank, degree=degree, seq_len=seq_len or q.shape[1] * degree, layout=layout, group=group,
                            mask=sparse if sparse is not None else MaskSpec(causal=causal))
-    if kv_fp8 is not None:
+    fp8_ring = ring.degree > 1 and q.is_cuda and getattr(ring.peer, "fp8_block_tokens", 0) > 0
+    if kv_fp8 is not None and not fp8_ring:
         k, v = kv_fp8.roundtrip(k), kv_fp8.roundtrip(v)
     return _RingAttnFn.apply(q, k, v, scale, ring)

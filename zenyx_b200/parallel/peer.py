@@ -97,29 +97,93 @@ class RingBuffers:
     * ``dkv``     2 slots x (dK, dV) fp32, peer-visible: where every rank adds its gradient share,
     * a flag barrier.
     Slots alternate between consecutive layers so one barrier per call is enough.
+
+    With ``fp8_block_tokens > 0`` the K/V slots and the staging buffers hold the e4m3 cache format instead of
+    bf16: per slot the K codes, the V codes (one byte per element) and their fp32 scales, one per (block of
+    ``fp8_block_tokens`` tokens, KV head). That halves the peer-visible K/V memory and the bytes every ring
+    step pulls over NVLink; the puller expands the staged codes to bf16 right before its attention kernel
+    (``dequant_staged``), so the tensor-core path itself still runs in bf16.
     """
 
-    def __init__(self, kv_shape: Sequence[int], group=None, timeout_ms: float = 20000.0, dtype=torch.bfloat16):
+    def __init__(self, kv_shape: Sequence[int], group=None, timeout_ms: float = 20000.0, dtype=torch.bfloat16,
+                 fp8_block_tokens: int = 0):
         self.kv_shape = tuple(kv_shape)
         n = 1
         for s in kv_shape:
             n *= s
         self.n = n
-        self.esize = _DTYPE_SIZE[dtype]
+        self.fp8_block_tokens = int(fp8_block_tokens)
         self.dtype = dtype
-        self.kv_bytes = n * self.esize            # one of K or V
         self.dkv_bytes = n * 4
-        self.kv = SymmetricBuffer(2 * 2 * self.kv_bytes, group)
+        if self.fp8_block_tokens > 0:
+            B, S, H, D = self.kv_shape
+            assert S % self.fp8_block_tokens == 0, "local sequence length must be a multiple of the fp8 block"
+            self.n_scales = B * (S // self.fp8_block_tokens) * H
+            self.kv_bytes = n                                              # codes of one of K or V
+            self.scale_bytes = (self.n_scales * 4 + 15) // 16 * 16         # scales of one of K or V
+            self.slot_bytes = (2 * self.kv_bytes + 2 * self.scale_bytes + 255) // 256 * 256
+            self.staging_raw = torch.empty(2, self.slot_bytes, device="cuda", dtype=torch.uint8)
+            self.work = torch.empty(2, n, device="cuda", dtype=dtype)      # dequantised K, V of the current step
+            self.staging = None
+        else:
+            self.esize = _DTYPE_SIZE[dtype]
+            self.kv_bytes = n * self.esize        # one of K or V
+            self.slot_bytes = 2 * self.kv_bytes
+            self.staging = torch.empty(2, 2, n, device="cuda", dtype=dtype)
+        self.kv = SymmetricBuffer(2 * self.slot_bytes, group)
         self.dkv = SymmetricBuffer(2 * 2 * self.dkv_bytes, group)
-        self.staging = torch.empty(2, 2, n, device="cuda", dtype=dtype)
         self.barrier_obj = PeerBarrier(group, timeout_ms)
         self.rank, self.world = self.kv.rank, self.kv.world
         self.C = self.kv.C
 
+    # e4m3 slots -----------------------------------------------------------------------------
+    def _q_layout(self, base_tensor_fn):
+        B, S, H, D = self.kv_shape
+        nb = S // self.fp8_block_tokens
+        kc = base_tensor_fn(0, (B * S, H, D), torch.uint8)
+        vc = base_tensor_fn(self.kv_bytes, (B * S, H, D), torch.uint8)
+        ks = base_tensor_fn(2 * self.kv_bytes, (B * nb, H), torch.float32)
+        vs = base_tensor_fn(2 * self.kv_bytes + self.scale_bytes, (B * nb, H), torch.float32)
+        return kc, vc, ks, vs
+
+    def quantize_into_slot(self, k: torch.Tensor, v: torch.Tensor, slot: int) -> None:
+        """Writes this rank's K and V (bf16 [B, S, Hkv, D]) into its slot as e4m3 codes + scales."""
+        base = slot * self.slot_bytes
+        kc, vc, ks, vs = self._q_layout(lambda off, shape, dt: self.kv.tensor(self.rank, base + off, shape, dt))
+        B, S, H, D = self.kv_shape
+        self.C.kv_quant_e4m3(k.reshape(B * S, H, D).contiguous(), kc, ks, None, self.fp8_block_tokens)
+        self.C.kv_quant_e4m3(v.reshape(B * S, H, D).contiguous(), vc, vs, None, self.fp8_block_tokens)
+
+    def _dequant(self, kc, vc, ks, vs) -> Tuple[torch.Tensor, torch.Tensor]:
+        B, S, H, D = self.kv_shape
+        kk, vv = self.work[0].view(B * S, H, D), self.work[1].view(B * S, H, D)
+        self.C.kv_dequant_e4m3(kc, ks, kk, self.fp8_block_tokens)
+        self.C.kv_dequant_e4m3(vc, vs, vv, self.fp8_block_tokens)
+        return kk.view(self.kv_shape), vv.view(self.kv_shape)
+
+    def dequant_local(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """bf16 K, V as every rank sees this rank's slot (the values the cache format can represent)."""
+        base = slot * self.slot_bytes
+        return self._dequant(*self._q_layout(lambda off, shape, dt: self.kv.tensor(self.rank, base + off, shape, dt)))
+
+    def dequant_staged(self, idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Expands the codes a previous kernel pulled into staging[idx] to bf16 K, V."""
+        raw = self.staging_raw[idx]
+
+        def view(off, shape, dt):
+            nbytes = 1
+            for d in shape:
+                nbytes *= d
+            nbytes *= _DTYPE_SIZE[dt]
+            return raw[off: off + nbytes].view(dt).view(shape)
+
+        return self._dequant(*self._q_layout(view))
+
     # K/V slot views -------------------------------------------------------------------------
     def kv_views(self, rank: int, slot: int, shape=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        assert self.fp8_block_tokens == 0, "e4m3 slots hold codes: use quantize_into_slot / dequant_*"
         shape = tuple(shape or self.kv_shape)
-        base = slot * 2 * self.kv_bytes
+        base = slot * self.slot_bytes
         return (self.kv.tensor(rank, base, shape, self.dtype),
                 self.kv.tensor(rank, base + self.kv_bytes, shape, self.dtype))
 
@@ -128,8 +192,12 @@ class RingBuffers:
         return self.staging[idx, 0].view(shape), self.staging[idx, 1].view(shape)
 
     def pull_args(self, owner: int, slot: int, stage: int) -> Tuple[int, int, int]:
-        """(src, dst, nbytes) copying owner's slot (K and V are adjacent) into staging[stage]."""
-        return (self.kv.ptr(owner, slot * 2 * self.kv_bytes), self.staging[stage].data_ptr(), 2 * self.kv_bytes)
+        """(src, dst, nbytes) copying owner's slot (K and V, in e4m3 mode also their scales, are adjacent) into
+        staging[stage]."""
+        if self.fp8_block_tokens > 0:
+            return (self.kv.ptr(owner, slot * self.slot_bytes), self.staging_raw[stage].data_ptr(),
+                    2 * self.kv_bytes + 2 * self.scale_bytes)
+        return (self.kv.ptr(owner, slot * self.slot_bytes), self.staging[stage].data_ptr(), 2 * self.kv_bytes)
 
     def pull_now(self, owner: int, slot: int, stage: int) -> None:
         src, dst, nbytes = self.pull_args(owner, slot, stage)

@@ -73,8 +73,11 @@ class QuantizedRingAttention(nn.Module):
     """Ring attention whose K/V pass through the e4m3 cache format.
 
     K and V are quantised once per call (after RoPE); every ring step then works on the quantised
-    values. In this version the bytes that cross NVLink are the dequantised bf16 tiles; the
-    tensor-core path still runs in bf16.
+    values. When the ``RingContext`` carries peer buffers built with ``fp8_block_tokens``
+    (``zenyx_b200.parallel.peer.RingBuffers``), the e4m3 codes and their scales are what sits in the
+    peer-visible slots and what each ring step pulls over NVLink (half the bytes of bf16); the pulling
+    rank expands them to bf16 right before its attention kernel. The tensor-core products themselves
+    run in bf16: an e4m3 ``kind::f8f6f4`` MMA path is not built.
     """
 
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int = 128, block_tokens: int = 128, group=None,
