@@ -222,20 +222,24 @@ def run_ours(args):
     except Exception:  # noqa: BLE001
         pass
     if args.ring_probe_steps > 0 and world > 1 and cp != world:
-        # secondary figure: the same step with the context-parallel ring over all GPUs (first probe step untimed)
-        eng.set_ring_degree(world)
-        pbase = args.warmup + args.steps
-        trainer.train_step(host_tokens[pbase], host_targets[pbase])
-        sync_all()
-        e0.record()
-        for i in range(1, args.ring_probe_steps):
-            trainer.train_step(host_tokens[pbase + i], host_targets[pbase + i])
-        e1.record()
-        sync_all()
-        if args.ring_probe_steps > 1:
-            ms_ring = max_over_ranks(e0.elapsed_time(e1)) / (args.ring_probe_steps - 1)
-            out["details"][f"ring_degree_{world}_tokens_per_s"] = round(B * S / (ms_ring / 1e3), 1)
-        _ext.check_status()
+        # secondary figure: the same step with the context-parallel ring over all GPUs (first probe step untimed);
+        # a failure here must not cost the main result
+        try:
+            eng.set_ring_degree(world)
+            pbase = args.warmup + args.steps
+            trainer.train_step(host_tokens[pbase], host_targets[pbase])
+            sync_all()
+            e0.record()
+            for i in range(1, args.ring_probe_steps):
+                trainer.train_step(host_tokens[pbase + i], host_targets[pbase + i])
+            e1.record()
+            sync_all()
+            if args.ring_probe_steps > 1:
+                ms_ring = max_over_ranks(e0.elapsed_time(e1)) / (args.ring_probe_steps - 1)
+                out["details"][f"ring_degree_{world}_tokens_per_s"] = round(B * S / (ms_ring / 1e3), 1)
+            _ext.check_status()
+        except Exception as e:  # noqa: BLE001
+            out["details"][f"ring_degree_{world}_probe_failed"] = f"{type(e).__name__}: {str(e)[:120]}"
     free_b, total_b = torch.cuda.mem_get_info()
     if memory_fallback:
         out["details"]["memory_fallback"] = memory_fallback

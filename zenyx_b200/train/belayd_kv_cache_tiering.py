@@ -153,7 +153,7 @@ class BeladyKVCacheTieringManager:
                  num_kv_heads: int = 8, head_dim: int = 128, dtype: torch.dtype = torch.bfloat16,
                  tier_block_tokens: Optional[int] = None, hbm_budget_bytes: int = 16 << 30,
                  dram_budget_bytes: Optional[int] = None, nvme_path: Optional[str] = None,
-                 simulate: Optional[bool] = None, rank: int = 0, lookahead: int = 4, sparse_pattern=None,
+                 simulate: Optional[bool] = None, rank: int = 0, lookahead: Optional[int] = None, sparse_pattern=None,
                  zigzag: bool = True):
         self.num_devices, self.context_length, self.num_layers = num_devices, context_length, num_layers
         self.num_kv_heads, self.head_dim, self.dtype, self.rank = num_kv_heads, head_dim, dtype, rank
@@ -171,6 +171,14 @@ class BeladyKVCacheTieringManager:
         self.dram_budget_bytes = dram_budget_bytes
         self.nvme_path = nvme_path
         self.simulate_mode = (not torch.cuda.is_available()) if simulate is None else bool(simulate)
+        # How many foreseen misses are kept in flight. The plan knows the whole future, so the depth is set by
+        # the slowest tier's latency, not by guesswork: pinned DRAM answers within one attention call (a few
+        # blocks suffice), a file read takes tens of them, and a shallow window there stalls the step for
+        # longer than the step itself. Bounded by an eighth of the HBM slots (they come out of the plan's budget).
+        if lookahead is None:
+            slots = max(1, int(hbm_budget_bytes) // max(1, 2 * tier_block_tokens * num_kv_heads * head_dim *
+                                                          torch.empty((), dtype=dtype).element_size()))
+            lookahead = max(2, min(32 if nvme_path is not None else 8, slots // 8))
         self.lookahead = lookahead
         self._seq = RingAttentionAccessSequence(num_devices, num_layers, self.blocks_per_layer, zigzag=zigzag,
                                                 sparse_pattern=sparse_pattern, seq_len=context_length)
