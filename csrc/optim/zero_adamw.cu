@@ -30,96 +30,121 @@ struct ZParams {
   float grad_scale, lr, beta1, beta2, eps, weight_decay, bias1, bias2;
 };
 
-__device__ __forceinline__ float4 ld_f4_stream(const float* p) {
-  float4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
 // NR: number of ranks known at compile time (1, 2, 4, 8), so the peer loads of one element are all in
 // flight together instead of one NVLink round trip after another; 0 = any count, loop at run time.
+//
+// Memory behaviour: per parameter the step moves 32 bytes through five streams of 8 or 16 bytes per thread. One
+// float4 group per thread per loop trip left the kernel at 0.23 of the copy rate: too few bytes in flight per SM for
+// HBM latency, and the loads sat behind `asm volatile` statements that the compiler may not reorder. Each thread now
+// handles UNROLL groups per trip, issues ALL of their loads (through the __ldcs intrinsic, which the compiler can
+// schedule) before the first dependent instruction, and the grid is sized to the work instead of capped.
+constexpr int ZERO_UNROLL = 2;
+
+struct Group {   // one float4 group of every stream
+  float4 g, mm, vv;
+  uint2 hi, lo;
+};
+
 template <int NR>
 __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
   __shared__ float s_red[8];
   const size_t nvec = p.n_shard >> 2;
   float local_ss = 0.f;
   const float clip = (p.do_update && p.clip_coef != nullptr) ? *p.clip_coef : 1.f;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t gi = p.shard_begin + (i << 2);  // global element index
-    float4 g;
-    if (p.do_reduce) {
-      g = make_float4(0.f, 0.f, 0.f, 0.f);
-      // start with the next rank so the R readers of one step hit R different owners
-      if constexpr (NR > 0) {
-        float* src[NR];
-        float4 a[NR];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  uint16_t* own_params = reinterpret_cast<uint16_t*>(p.params.p[p.rank]);
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * ZERO_UNROLL) {
+    Group u[ZERO_UNROLL];
+    bool live[ZERO_UNROLL];
+    // ---- all loads of this trip ----
 #pragma unroll
-        for (int k = 0; k < NR; ++k) {
-          int r = p.rank + 1 + k;
-          if (r >= NR) r -= NR;
-          src[k] = reinterpret_cast<float*>(p.grads.p[r]) + gi;
+    for (int q = 0; q < ZERO_UNROLL; ++q) {
+      const size_t i = i0 + (size_t)q * stride;
+      live[q] = i < nvec;
+      if (!live[q]) continue;
+      const size_t gi = p.shard_begin + (i << 2);  // global element index
+      if (p.do_reduce) {
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        // start with the next rank so the R readers of one step hit R different owners
+        if constexpr (NR > 0) {
+          float4 a[NR];
+#pragma unroll
+          for (int k = 0; k < NR; ++k) {
+            int r = p.rank + 1 + k;
+            if (r >= NR) r -= NR;
+            a[k] = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<float*>(p.grads.p[r]) + gi));
+          }
+#pragma unroll
+          for (int k = 0; k < NR; ++k) { g.x += a[k].x; g.y += a[k].y; g.z += a[k].z; g.w += a[k].w; }
+        } else {
+          for (int k = 0; k < p.nranks; ++k) {
+            int r = p.rank + 1 + k;
+            if (r >= p.nranks) r -= p.nranks;
+            const float4 a = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<float*>(p.grads.p[r]) + gi));
+            g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+          }
         }
-#pragma unroll
-        for (int k = 0; k < NR; ++k) a[k] = ld_f4_stream(src[k]);
-#pragma unroll
-        for (int k = 0; k < NR; ++k) {
-          g.x += a[k].x; g.y += a[k].y; g.z += a[k].z; g.w += a[k].w;
-          if (p.zero_grads) *reinterpret_cast<float4*>(src[k]) = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        u[q].g = g;
       } else {
-        for (int k = 0; k < p.nranks; ++k) {
-          int r = p.rank + 1 + k;
-          if (r >= p.nranks) r -= p.nranks;
-          float* src = reinterpret_cast<float*>(p.grads.p[r]) + gi;
-          const float4 a = ld_f4_stream(src);
-          g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-          if (p.zero_grads) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+        u[q].g = __ldcs(reinterpret_cast<const float4*>(p.g_shard) + i);
+      }
+      if (p.do_update) {
+        u[q].hi = *reinterpret_cast<const uint2*>(own_params + gi);
+        u[q].lo = reinterpret_cast<const uint2*>(p.p_lo)[i];
+        u[q].mm = reinterpret_cast<const float4*>(p.m)[i];
+        u[q].vv = reinterpret_cast<const float4*>(p.v)[i];
+      }
+    }
+    // ---- arithmetic and stores ----
+#pragma unroll
+    for (int q = 0; q < ZERO_UNROLL; ++q) {
+      if (!live[q]) continue;
+      const size_t i = i0 + (size_t)q * stride;
+      const size_t gi = p.shard_begin + (i << 2);
+      float4 g = u[q].g;
+      if (p.do_reduce) {
+        if (p.zero_grads) {
+          const int nr = NR > 0 ? NR : p.nranks;
+          for (int r = 0; r < nr; ++r)
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.grads.p[r]) + gi) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        g.x *= p.grad_scale; g.y *= p.grad_scale; g.z *= p.grad_scale; g.w *= p.grad_scale;
+        local_ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+        if (!p.do_update) {   // norm pass: keep the reduced shard if there is room for it, else only its norm
+          if (p.g_shard != nullptr) reinterpret_cast<float4*>(p.g_shard)[i] = g;
+          continue;
         }
       }
-      g.x *= p.grad_scale; g.y *= p.grad_scale; g.z *= p.grad_scale; g.w *= p.grad_scale;
-      local_ss += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
-      if (!p.do_update) {   // norm pass: keep the reduced shard if there is room for it, else only its norm
-        if (p.g_shard != nullptr) reinterpret_cast<float4*>(p.g_shard)[i] = g;
-        continue;
-      }
-    } else {
-      g = reinterpret_cast<const float4*>(p.g_shard)[i];
-    }
-    // ---- AdamW on the split master ----
-    g.x *= clip; g.y *= clip; g.z *= clip; g.w *= clip;
-    uint16_t* own_params = reinterpret_cast<uint16_t*>(p.params.p[p.rank]);
-    const uint2 hi = *reinterpret_cast<const uint2*>(own_params + gi);
-    const uint2 lo = reinterpret_cast<const uint2*>(p.p_lo)[i];
-    float4 mm = reinterpret_cast<float4*>(p.m)[i];
-    float4 vv = reinterpret_cast<float4*>(p.v)[i];
-    const uint16_t h[4] = {(uint16_t)(hi.x & 0xffff), (uint16_t)(hi.x >> 16), (uint16_t)(hi.y & 0xffff), (uint16_t)(hi.y >> 16)};
-    const int16_t l[4] = {(int16_t)(lo.x & 0xffff), (int16_t)(lo.x >> 16), (int16_t)(lo.y & 0xffff), (int16_t)(lo.y >> 16)};
-    float gr[4] = {g.x, g.y, g.z, g.w};
-    float ma[4] = {mm.x, mm.y, mm.z, mm.w};
-    float va[4] = {vv.x, vv.y, vv.z, vv.w};
-    const float wd = gi < p.decay_end ? p.weight_decay : 0.f;
-    uint32_t nh[4], nl[4];
+      // ---- AdamW on the split master ----
+      g.x *= clip; g.y *= clip; g.z *= clip; g.w *= clip;
+      const uint2 hi = u[q].hi, lo = u[q].lo;
+      const float4 mm = u[q].mm, vv = u[q].vv;
+      const uint16_t h[4] = {(uint16_t)(hi.x & 0xffff), (uint16_t)(hi.x >> 16), (uint16_t)(hi.y & 0xffff), (uint16_t)(hi.y >> 16)};
+      const int16_t l[4] = {(int16_t)(lo.x & 0xffff), (int16_t)(lo.x >> 16), (int16_t)(lo.y & 0xffff), (int16_t)(lo.y >> 16)};
+      float gr[4] = {g.x, g.y, g.z, g.w};
+      float ma[4] = {mm.x, mm.y, mm.z, mm.w};
+      float va[4] = {vv.x, vv.y, vv.z, vv.w};
+      const float wd = gi < p.decay_end ? p.weight_decay : 0.f;
+      uint32_t nh[4], nl[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float w = __uint_as_float(((uint32_t)h[j] << 16) + (uint32_t)(int32_t)l[j]);
-      ma[j] = p.beta1 * ma[j] + (1.f - p.beta1) * gr[j];
-      va[j] = p.beta2 * va[j] + (1.f - p.beta2) * gr[j] * gr[j];
-      w = w * (1.f - p.lr * wd) - p.lr * (ma[j] / p.bias1) / (sqrtf(va[j] / p.bias2) + p.eps);
-      const uint32_t bits = __float_as_uint(w);
-      const uint32_t hh = (bits + 0x8000u) >> 16;
-      nh[j] = hh & 0xffffu;
-      nl[j] = (bits - (hh << 16)) & 0xffffu;
+      for (int j = 0; j < 4; ++j) {
+        float w = __uint_as_float(((uint32_t)h[j] << 16) + (uint32_t)(int32_t)l[j]);
+        ma[j] = p.beta1 * ma[j] + (1.f - p.beta1) * gr[j];
+        va[j] = p.beta2 * va[j] + (1.f - p.beta2) * gr[j] * gr[j];
+        w = w * (1.f - p.lr * wd) - p.lr * (ma[j] / p.bias1) / (sqrtf(va[j] / p.bias2) + p.eps);
+        const uint32_t bits = __float_as_uint(w);
+        const uint32_t hh = (bits + 0x8000u) >> 16;
+        nh[j] = hh & 0xffffu;
+        nl[j] = (bits - (hh << 16)) & 0xffffu;
+      }
+      reinterpret_cast<float4*>(p.m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+      reinterpret_cast<float4*>(p.v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+      reinterpret_cast<uint2*>(p.p_lo)[i] = make_uint2(nl[0] | (nl[1] << 16), nl[2] | (nl[3] << 16));
+      const uint2 new_hi = make_uint2(nh[0] | (nh[1] << 16), nh[2] | (nh[3] << 16));
+      // all-gather: push the new bf16 parameters into every rank's buffer
+      for (int r = 0; r < p.nranks; ++r)
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.params.p[r]) + gi) = new_hi;
     }
-    reinterpret_cast<float4*>(p.m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
-    reinterpret_cast<float4*>(p.v)[i] = make_float4(va[0], va[1], va[2], va[3]);
-    reinterpret_cast<uint2*>(p.p_lo)[i] = make_uint2(nl[0] | (nl[1] << 16), nl[2] | (nl[3] << 16));
-    const uint2 new_hi = make_uint2(nh[0] | (nh[1] << 16), nh[2] | (nh[3] << 16));
-    // all-gather: push the new bf16 parameters into every rank's buffer
-    for (int r = 0; r < p.nranks; ++r)
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.params.p[r]) + gi) = new_hi;
   }
   if (p.do_reduce && p.sumsq != nullptr) {
 #pragma unroll
@@ -150,8 +175,8 @@ void launch_zero_step(const ZeroArgs& a) {
   p.bias1 = 1.f - powf(a.beta1, (float)a.step);
   p.bias2 = 1.f - powf(a.beta2, (float)a.step);
   const size_t nvec = a.n_shard / 4;
-  size_t blocks = (nvec + 255) / 256;
-  const size_t cap = (size_t)a.sm_count * 8;
+  size_t blocks = (nvec + 256 * ZERO_UNROLL - 1) / (256 * ZERO_UNROLL);
+  const size_t cap = (size_t)a.sm_count * 64;   // several waves: the tail of one hides under the head of the next
   if (blocks > cap) blocks = cap;
   switch (a.nranks) {
     case 1: zero_step_kernel<1><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;

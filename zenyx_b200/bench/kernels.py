@@ -106,6 +106,24 @@ def bench_attn(S, Hq=32, Hkv=8, B=1, causal=True, bwd=True, iters=5, warmup=3):
     return out
 
 
+def bench_zero(n_params=64 << 20):
+    """The sharded-optimizer step on one GPU (no peers): per parameter it reads an fp32 gradient, the bf16 + int16
+    halves of the master weight and fp32 m, v, writes all but the gradient back and clears the gradient: 32 bytes."""
+    from zenyx_b200.models.llama import FlatBuffers
+    from zenyx_b200.ops import _ext
+    from zenyx_b200.parallel.zero import ZeroAdamW
+
+    rows = n_params // 8192
+    flat = FlatBuffers([("w", (rows, 8192), True)], "cuda")
+    opt = ZeroAdamW(flat, lr=1e-3)
+    flat.grads.normal_()
+    ms = time_cuda(lambda: opt.step(), iters=10)
+    _ext.check_status()
+    gbs = flat.total * 32 / ms / 1e6
+    return {"kernel": "zero_adamw step (1 GPU)", "params": flat.total, "ms": round(ms, 4), "gbs": round(gbs, 1),
+            "frac_of_copy_rate": round(gbs / peaks()["gbs"], 3), "peak": peaks()["source"]}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
@@ -115,6 +133,7 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, nargs="*", default=None, help="attention sequence lengths (default 8192 32768)")
     ap.add_argument("--attn-iters", type=int, default=5, help="timed attention launches (1 for a profiler capture)")
     ap.add_argument("--attn-warmup", type=int, default=3)
+    ap.add_argument("--zero", action="store_true", help="also time the optimizer step kernel")
     args = ap.parse_args(argv)
     shapes = [(8192, 8192, 8192, False, False)]
     if not args.quick:
@@ -127,6 +146,8 @@ def main(argv=None):
         ]
     for M, N, K, at, bt in ([] if args.no_gemm else shapes):
         print(json.dumps(bench_gemm(M, N, K, at, bt)), flush=True)
+    if args.zero:
+        print(json.dumps(bench_zero()), flush=True)
     if not args.no_attn:
         for S in (args.seq or ([8192] if args.quick else [8192, 32768])):
             for rec in bench_attn(S, bwd=not args.no_bwd, iters=args.attn_iters, warmup=args.attn_warmup):
