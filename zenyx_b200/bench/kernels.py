@@ -124,6 +124,40 @@ def bench_zero(n_params=64 << 20):
             "frac_of_copy_rate": round(gbs / peaks()["gbs"], 3), "peak": peaks()["source"]}
 
 
+def bench_fused(tokens=32768, H=4096, F=14336, Hq=32, Hkv=8, D=128):
+    """Achieved HBM rate of the bandwidth-bound kernels of a Llama block at the 8B shape (algorithmic bytes / time)."""
+    from zenyx_b200.ops import _ext, fused
+
+    out = []
+    gbs_peak = peaks()["gbs"]
+
+    def rec(name, nbytes, fn):
+        ms = time_cuda(fn, iters=10)
+        _ext.check_status()
+        out.append({"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+                    "frac_of_copy_rate": round(nbytes / ms / 1e6 / gbs_peak, 3)})
+
+    x = torch.randn(tokens, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    y, rstd = fused.rmsnorm_fwd(x, w, 1e-5)
+    rec("rmsnorm_fwd", 2 * x.numel() * 2, lambda: fused.rmsnorm_fwd(x, w, 1e-5))
+    dw = torch.zeros(H, device="cuda")
+    rec("rmsnorm_bwd (+residual gradient)", 4 * x.numel() * 2, lambda: fused.rmsnorm_bwd(y, x, w, rstd, dw, x))
+    gu = torch.randn(tokens, 2 * F, device="cuda").bfloat16()
+    h = fused.swiglu_fwd(gu)
+    rec("swiglu_fwd", 3 * tokens * F * 2, lambda: fused.swiglu_fwd(gu))
+    rec("swiglu_bwd", 5 * tokens * F * 2, lambda: fused.swiglu_bwd(gu, h))
+    qkv = torch.randn(tokens, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    cos, sin = fused.rope_tables(torch.arange(tokens, device="cuda"), D, 500000.0)
+    rec("rope_qkv (in place)", 2 * tokens * (Hq + Hkv) * D * 2, lambda: fused.rope_qkv_(qkv, cos, sin, Hq, Hkv, D, tokens))
+    dq = torch.randn(tokens, Hq, D, device="cuda")
+    dk = torch.randn(tokens, Hkv, D, device="cuda")
+    dv = torch.randn(tokens, Hkv, D, device="cuda")
+    rec("rope_bwd_pack (fp32 dq, dk, dv -> bf16 dqkv)", tokens * (Hq + 2 * Hkv) * D * 6,
+        lambda: fused.rope_bwd_pack(dq, dk, dv, cos, sin, Hq, Hkv, D, tokens))
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
@@ -134,6 +168,7 @@ def main(argv=None):
     ap.add_argument("--attn-iters", type=int, default=5, help="timed attention launches (1 for a profiler capture)")
     ap.add_argument("--attn-warmup", type=int, default=3)
     ap.add_argument("--zero", action="store_true", help="also time the optimizer step kernel")
+    ap.add_argument("--fused", action="store_true", help="also time the bandwidth-bound kernels of a Llama block")
     args = ap.parse_args(argv)
     shapes = [(8192, 8192, 8192, False, False)]
     if not args.quick:
@@ -148,6 +183,9 @@ def main(argv=None):
         print(json.dumps(bench_gemm(M, N, K, at, bt)), flush=True)
     if args.zero:
         print(json.dumps(bench_zero()), flush=True)
+    if args.fused:
+        for rec in bench_fused():
+            print(json.dumps(rec), flush=True)
     if not args.no_attn:
         for S in (args.seq or ([8192] if args.quick else [8192, 32768])):
             for rec in bench_attn(S, bwd=not args.no_bwd, iters=args.attn_iters, warmup=args.attn_warmup):
