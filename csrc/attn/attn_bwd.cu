@@ -230,11 +230,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Head-major: the CTAs in flight then share one or two heads' Q and dO tiles in L2 (measured 2 % faster than
+  // spreading them over all heads). Inside a head, early KV tiles (most work under a causal mask) run first.
   int bid = blockIdx.x;
-  const int hk = bid % p.Hkv;
-  bid /= p.Hkv;
+  const int j = bid % p.n_kv_tiles;
+  bid /= p.n_kv_tiles;
   const int b = bid % p.B;
-  const int j = bid / p.B;  // KV tile; early tiles (most work under a causal mask) run first
+  const int hk = bid / p.B;
   const int G = p.Hq / p.Hkv;
   const int kpos0 = kv_tile_pos(p, j);
 
@@ -589,11 +591,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Head-major, late Q tiles (most work) first inside a head: the CTAs in flight stream the same K and V.
   int bid = blockIdx.x;
-  const int hq = bid % p.Hq;
-  bid /= p.Hq;
+  const int t = p.n_q_tiles - 1 - bid % p.n_q_tiles;
+  bid /= p.n_q_tiles;
   const int b = bid % p.B;
-  const int t = p.n_q_tiles - 1 - bid / p.B;  // late Q tiles (most work) first
+  const int hq = bid / p.B;
   const int hk = hq / (p.Hq / p.Hkv);
   const int qpos0 = q_tile_pos(p, t);
 

@@ -61,10 +61,10 @@ class _CountingProxy:
             raw = getattr(self._mod, name)
             n = _LAUNCHES.get(name, 1)
 
-            def fn(*args, __raw=raw, __n=n):
+            def fn(*args, __raw=raw, __n=n, **kwargs):
                 global launch_count
                 launch_count += __n
-                return __raw(*args)
+                return __raw(*args, **kwargs)
 
             self._cache[name] = fn
         return fn
