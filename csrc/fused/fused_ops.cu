@@ -67,6 +67,46 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
+
+// Same, for rows of 32 * VPL vectors: the row is loaded once, all loads of a lane in flight together, and
+// stays in registers between the sum of squares and the scaling.
+template <int VPL>
+__global__ void __launch_bounds__(128, 3) rmsnorm_fwd_regs_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                               int rows, float eps) {
+  constexpr int H = VPL * 32 * 8;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+  uint4 v[VPL];
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) v[k] = __ldcs(xr + lane + 32 * k);
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    float f[8];
+    unpack8(v[k], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)H + eps);
+  if (lane == 0 && rstd != nullptr) rstd[row] = r;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    float f[8], g[8];
+    unpack8(v[k], f);
+    unpack8(__ldg(wr + lane + 32 * k), g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * r * g[j];
+    yr[lane + 32 * k] = pack8(f);
+  }
+}
+
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw += sum_rows dy * xhat (fp32 atomics per block).
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -116,6 +156,106 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
   }
   __syncthreads();
   for (int i = threadIdx.x; i < H; i += blockDim.x) atomicAdd(&dw_accum[i], s_dw[i]);
+}
+
+
+// Same result for rows of up to 512 * VPT vectors, one block of 512 threads per group of R rows: thread i owns
+// vectors i, i + 512, ... of every row, so its share of dw stays in registers for the whole kernel (one global
+// reduction per column and block at the end, no shared-memory atomics), each row is read once, and the R rows
+// of a group are loaded together (2 R VPT 16-byte loads in flight per thread).
+template <int VPT, int R>
+__global__ void __launch_bounds__(512) rmsnorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                               const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               const float* __restrict__ rstd,
+                                                               const __nv_bfloat16* __restrict__ dres,
+                                                               __nv_bfloat16* __restrict__ dx,
+                                                               float* __restrict__ dw_accum, int rows, int H) {
+  __shared__ float red[2][R][16];
+  const int nvec = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float fw[VPT][8], dw[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + 512 * k;
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (i < nvec) wv = __ldg(reinterpret_cast<const uint4*>(w) + i);
+    unpack8(wv, fw[k]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[k][j] = 0.f;
+  }
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, ++it) {
+    uint4 xv[R][VPT], dv[R][VPT];
+    float rs[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const int row = row0 + q;
+      rs[q] = row < rows ? rstd[row] : 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + 512 * k;
+        const bool in = row < rows && i < nvec;
+        xv[q][k] = in ? __ldcs(reinterpret_cast<const uint4*>(x + (size_t)row * H) + i) : make_uint4(0, 0, 0, 0);
+        dv[q][k] = in ? __ldcs(reinterpret_cast<const uint4*>(dy + (size_t)row * H) + i) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    float dot[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      float a = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        float fx[8], fd[8];
+        unpack8(xv[q][k], fx);
+        unpack8(dv[q][k], fd);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a += fd[j] * fw[k][j] * fx[j];
+      }
+      a = warp_sum(a);
+      if (lane == 0) red[it & 1][q][warp] = a;
+    }
+    __syncthreads();   // red[] of this parity is next written two iterations later, behind the next barrier
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      float a = lane < 16 ? red[it & 1][q][lane] : 0.f;
+      dot[q] = warp_sum(a) * rs[q] / (float)H;
+    }
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const int row = row0 + q;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + 512 * k;
+        if (row < rows && i < nvec) {
+          float fx[8], fd[8], o[8];
+          unpack8(xv[q][k], fx);
+          unpack8(dv[q][k], fd);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float xh = fx[j] * rs[q];
+            o[j] = rs[q] * (fd[j] * fw[k][j] - xh * dot[q]);
+            dw[k][j] += fd[j] * xh;
+          }
+          if (dres != nullptr) {  // gradient arriving through the residual branch
+            float fr[8];
+            unpack8(__ldcs(reinterpret_cast<const uint4*>(dres + (size_t)row * H) + i), fr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += fr[j];
+          }
+          reinterpret_cast<uint4*>(dx + (size_t)row * H)[i] = pack8(o);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + 512 * k;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&dw_accum[i * 8 + j], dw[k][j]);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -541,19 +681,42 @@ void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int 
                         cudaStream_t st) {
   if (rows == 0) return;
   const int wpb = 4;
-  rmsnorm_fwd_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                               (__nv_bfloat16*)y, rstd, rows, H, eps);
+  const unsigned grid = (rows + wpb - 1) / wpb;
+  auto xb = (const __nv_bfloat16*)x;
+  auto wb = (const __nv_bfloat16*)w;
+  auto yb = (__nv_bfloat16*)y;
+  switch (H) {
+    case 2048: rmsnorm_fwd_regs_kernel<8><<<grid, wpb * 32, 0, st>>>(xb, wb, yb, rstd, rows, eps); break;
+    case 4096: rmsnorm_fwd_regs_kernel<16><<<grid, wpb * 32, 0, st>>>(xb, wb, yb, rstd, rows, eps); break;
+    default: rmsnorm_fwd_kernel<<<grid, wpb * 32, 0, st>>>(xb, wb, yb, rstd, rows, H, eps);
+  }
 }
 void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                         float* dw_accum, int rows, int H, int sm_count, cudaStream_t st) {
   if (rows == 0) return;
+  auto dyb = (const __nv_bfloat16*)dy;
+  auto xb = (const __nv_bfloat16*)x;
+  auto wb = (const __nv_bfloat16*)w;
+  auto rb = (const __nv_bfloat16*)dres;
+  auto dxb = (__nv_bfloat16*)dx;
+  const int nvec = H / 8;
+  if (nvec <= 1024) {
+    // one resident block of 512 threads per SM (the row group lives in registers): a persistent grid
+    const int R = nvec <= 512 ? 4 : 2;
+    int grid = sm_count;
+    const int max_grid = (rows + R - 1) / R;
+    if (grid > max_grid) grid = max_grid;
+    if (nvec <= 512)
+      rmsnorm_bwd_cols_kernel<1, 4><<<grid, 512, 0, st>>>(dyb, xb, wb, rstd, rb, dxb, dw_accum, rows, H);
+    else
+      rmsnorm_bwd_cols_kernel<2, 2><<<grid, 512, 0, st>>>(dyb, xb, wb, rstd, rb, dxb, dw_accum, rows, H);
+    return;
+  }
   const int threads = 256;
   int grid = sm_count * 4;
   const int max_grid = (rows + 7) / 8;
   if (grid > max_grid) grid = max_grid;
-  rmsnorm_bwd_kernel<<<grid, threads, H * sizeof(float), st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                              (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-                                                              (__nv_bfloat16*)dx, dw_accum, rows, H);
+  rmsnorm_bwd_kernel<<<grid, threads, H * sizeof(float), st>>>(dyb, xb, wb, rstd, rb, dxb, dw_accum, rows, H);
 }
 void launch_rope_qkv(void* qkv, const float* cos_t, const float* sin_t, void* k_out, void* v_out, int tokens,
                      int tokens_per_seq, int Hq, int Hkv, int D, float sign, int sm_count, cudaStream_t st) {

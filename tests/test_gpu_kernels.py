@@ -196,9 +196,10 @@ def test_attn_fwd_block_sparse(C):
     assert (lse - lse_ref).abs().max().item() < 2e-2
 
 
-def test_rmsnorm(C):
+@pytest.mark.parametrize("rows,H", [(777, 4096), (130, 2048), (33, 1024), (50, 6144), (9, 8192 + 512)])
+def test_rmsnorm(C, rows, H):
+    # 4096 / 2048: row-in-registers forward; H <= 4096: one vector per thread backward, <= 8192: two, above: fallback
     torch.manual_seed(6)
-    rows, H = 777, 4096
     x = torch.randn(rows, H, device="cuda").bfloat16()
     w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
     y = torch.empty_like(x)
@@ -208,6 +209,7 @@ def test_rmsnorm(C):
     wf = w.float().requires_grad_(True)
     ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
     assert _rel_err(y, ref) < 1e-2
+    assert _rel_err(rstd, torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5)) < 1e-4
     dy = torch.randn_like(x)
     ref.backward(dy.float())
     dx = torch.empty_like(x)
@@ -215,6 +217,13 @@ def test_rmsnorm(C):
     C.rmsnorm_bwd(dy, x, w, rstd, dx, dw, None)
     assert _rel_err(dx, xf.grad) < 1e-2
     assert _rel_err(dw, wf.grad) < 1e-2
+    # with the gradient of the residual branch added in, and dw accumulating on top of the first call
+    dres = torch.randn_like(x)
+    dx2 = torch.empty_like(x)
+    C.rmsnorm_bwd(dy, x, w, rstd, dx2, dw, dres)
+    assert _rel_err(dx2, xf.grad + dres.float()) < 1e-2
+    assert _rel_err(dw, 2 * wf.grad) < 1e-2
+    _status_ok()
 
 
 def test_swiglu(C):
