@@ -28,7 +28,12 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;    // one 64-wide MN chunk of an MN-maj
 constexpr int NUM_THREADS = 224;   // TMA, MMA, four epilogue warps, one peer-pull warp
 constexpr int W_PULL = 6;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+// Output staging for the TMA-store epilogue: per epilogue warp two slabs of 32 rows x 64 bf16 columns (128-byte
+// rows, 128-byte swizzle), written from registers and handed to cp.async.bulk.tensor stores.
+constexpr int SLAB_BYTES = 32 * 128;
+constexpr int STAGING_BYTES = 4 * 2 * SLAB_BYTES;   // 32 KB
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+static_assert(SMEM_BYTES <= 227 * 1024, "gemm shared memory");
 
 struct KParams {
   int M, N, K;
@@ -37,6 +42,7 @@ struct KParams {
   const void* D;
   int out_fp32;
   int d_mode;  // 0: none, 1: bf16 addend, 2: fp32 addend
+  int tma_store;  // plain bf16 output: the epilogue goes through shared memory and TMA stores
   int num_m, num_n;
   const uint4* pull_src;
   uint4* pull_dst;
@@ -59,18 +65,21 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, KParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* sStage = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);   // 1024-byte aligned: STAGES * 48 KB above smem
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStage + STAGING_BYTES);
   uint64_t* full = bars;                 // [STAGES]
   uint64_t* empty = bars + STAGES;       // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;      // [2]
   uint64_t* acc_empty = bars + 2 * STAGES + 2; // [2]
   uint64_t* drain_bar = bars + 2 * STAGES + 4; // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  uint64_t* d_full = bars + 2 * STAGES + 5;    // [4] addend slab of epilogue warp q has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -88,6 +97,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&acc_empty[b], 4);   // one arrival per epilogue warp
     }
     mbar_init(drain_bar, 1);
+    for (int w = 0; w < 4; ++w) mbar_init(&d_full[w], 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -192,6 +202,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------- epilogue warps -----------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t lt = 0;
+    uint32_t d_phase = 0;    // parity of this warp's addend barrier
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
       int tm, tn;
@@ -201,6 +212,78 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
+      if (p.tma_store) {
+        // Thread-per-row stores put 16 bytes of 32 different rows into every store instruction, and the L2 traffic
+        // of those partial sectors cost the main loop 4-17 % of its throughput. Here each 64-column chunk of the
+        // warp's 32 rows is packed to bf16, written to a swizzled slab in shared memory (chunk c of row r at
+        // position c ^ (r % 8): conflict-free per quarter warp) and stored by the TMA unit as whole 128-byte
+        // lines; the unit also clips rows and columns beyond the matrix.
+        // A bf16 addend takes the same road in the other direction: its slab is loaded by the TMA unit into the
+        // staging slab (rows and columns beyond the matrix read as zero) while the accumulator is unpacked.
+        uint8_t* slabs = sStage + q * 2 * SLAB_BYTES;
+        if (tm * BM + q * 32 < p.M) {
+#pragma unroll 1
+          for (int cc = 0; cc < BN / 64; ++cc) {
+            const int col0 = tn * BN + cc * 64;
+            if (col0 >= p.N) break;
+            uint8_t* slab = slabs + (cc & 1) * SLAB_BYTES;
+            if (lane == 0) {
+              tma_store_wait_read<1>();   // the store that read this slab two chunks ago is done with it
+              if (p.d_mode == 1) {
+                mbar_expect_tx(&d_full[q], SLAB_BYTES);
+                tma_load_2d(slab, &tmD, &d_full[q], col0, tm * BM + q * 32);
+              }
+            }
+            __syncwarp();   // lane 0 has seen the slab free
+            uint8_t* srow = slab + lane * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(tmem_addr(tmem_base, q * 32, buf * BN + cc * 64 + h * 32), r);
+              tmem_wait_ld();
+              if (p.d_mode == 1) {
+                if (h == 0) {
+                  if (!mbar_wait(&d_full[q], d_phase, abort_flag)) { ok = false; break; }
+                  d_phase ^= 1u;
+                }
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {   // fp32 accumulator + addend, rounded to bf16 once
+                  uint4* cell = reinterpret_cast<uint4*>(srow + (((h * 4 + c4) ^ (lane & 7)) << 4));
+                  const uint4 d = *cell;
+                  const float2 a0 = unpack_bf16x2(d.x), a1 = unpack_bf16x2(d.y), a2 = unpack_bf16x2(d.z),
+                               a3 = unpack_bf16x2(d.w);
+                  const uint32_t* f = r + 8 * c4;
+                  *cell = make_uint4(pack_bf16x2(__uint_as_float(f[0]) + a0.x, __uint_as_float(f[1]) + a0.y),
+                                     pack_bf16x2(__uint_as_float(f[2]) + a1.x, __uint_as_float(f[3]) + a1.y),
+                                     pack_bf16x2(__uint_as_float(f[4]) + a2.x, __uint_as_float(f[5]) + a2.y),
+                                     pack_bf16x2(__uint_as_float(f[6]) + a3.x, __uint_as_float(f[7]) + a3.y));
+                }
+              } else {
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                  const uint32_t* f = r + 8 * c4;
+                  *reinterpret_cast<uint4*>(srow + (((h * 4 + c4) ^ (lane & 7)) << 4)) =
+                      make_uint4(pack_bf16x2(__uint_as_float(f[0]), __uint_as_float(f[1])),
+                                 pack_bf16x2(__uint_as_float(f[2]), __uint_as_float(f[3])),
+                                 pack_bf16x2(__uint_as_float(f[4]), __uint_as_float(f[5])),
+                                 pack_bf16x2(__uint_as_float(f[6]), __uint_as_float(f[7])));
+                }
+              }
+            }
+            if (!ok) break;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmC, slab, col0, tm * BM + q * 32);
+              tma_store_commit();
+            }
+          }
+        }
+        if (!ok) break;
+        tc_fence_before();
+        mbar_arrive_warp(&acc_empty[buf]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -275,6 +358,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_arrive_warp(&acc_empty[buf]);
     }
     if (!ok && lane == 0) report(p.status, ZX_ERR_TIMEOUT, /*site=*/3, (int)lt);
+    if (p.tma_store && lane == 0) tma_store_wait<0>();   // shared memory must outlive the stores that read it
   }
 
   // ------------------------------- teardown -------------------------------------
@@ -287,7 +371,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <bool A_MN, bool B_MN>
-void launch_variant(const GemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& p, int grid) {
+void launch_variant(const GemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                    const CUtensorMap& tmD, const KParams& p, int grid) {
   static PerDeviceOnce once;
   bool& configured = once.current();
   auto kern = gemm_bf16_kernel<A_MN, B_MN>;
@@ -296,7 +381,7 @@ void launch_variant(const GemmArgs& a, const CUtensorMap& tmA, const CUtensorMap
     if (e != cudaSuccess) throw std::runtime_error(std::string("gemm: cannot raise shared memory limit: ") + cudaGetErrorString(e));
     configured = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, a.stream>>>(tmA, tmB, p);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, a.stream>>>(tmA, tmB, tmC, tmD, p);
 }
 
 }  // namespace
@@ -331,6 +416,10 @@ void launch_gemm_bf16(const GemmArgs& a) {
   p.ldc = a.ldc; p.ldd = a.ldd;
   p.C = a.C; p.D = a.D;
   p.out_fp32 = a.out_fp32; p.d_mode = a.d_mode;
+  p.tma_store = (!a.out_fp32 && a.d_mode != 2 && a.scatter_ranks == 0) ? 1 : 0;
+  // box: 64 columns (one 128-byte swizzle span) x the 32 rows of one epilogue warp
+  CUtensorMap tmC = p.tma_store ? make_tma_2d(a.C, 2, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc, 64, 32) : tmA;
+  CUtensorMap tmD = (p.tma_store && a.d_mode == 1) ? make_tma_2d(a.D, 2, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldd, 64, 32) : tmA;
   p.num_m = (a.M + BM - 1) / BM;
   p.num_n = (a.N + BN - 1) / BN;
   p.pull_src = reinterpret_cast<const uint4*>(a.pull_src);
@@ -344,11 +433,11 @@ void launch_gemm_bf16(const GemmArgs& a) {
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < a.sm_count ? tiles : a.sm_count;
   if (a.a_mn) {
-    if (a.b_mn) launch_variant<true, true>(a, tmA, tmB, p, grid);
-    else launch_variant<true, false>(a, tmA, tmB, p, grid);
+    if (a.b_mn) launch_variant<true, true>(a, tmA, tmB, tmC, tmD, p, grid);
+    else launch_variant<true, false>(a, tmA, tmB, tmC, tmD, p, grid);
   } else {
-    if (a.b_mn) launch_variant<false, true>(a, tmA, tmB, p, grid);
-    else launch_variant<false, false>(a, tmA, tmB, p, grid);
+    if (a.b_mn) launch_variant<false, true>(a, tmA, tmB, tmC, tmD, p, grid);
+    else launch_variant<false, false>(a, tmA, tmB, tmC, tmD, p, grid);
   }
 }
 

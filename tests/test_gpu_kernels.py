@@ -64,6 +64,28 @@ def test_gemm_layouts(C, a_t, b_t, M, N, K):
     assert _rel_err(out3, ref + res.float()) < 1e-2
 
 
+@pytest.mark.parametrize("with_addend", [False, True])
+@pytest.mark.parametrize("M,N,K", [(1000, 264, 136), (130, 72, 64), (257, 512, 320)])
+def test_gemm_output_view_leaves_its_surroundings_alone(C, M, N, K, with_addend):
+    """bf16 output (and addend) as a window of a larger matrix: the epilogue's TMA stores clip at the window's
+    edge, and the addend's TMA loads read zeros beyond it instead of the neighbouring values."""
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    big = torch.full((M + 3, N + 24), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = big[1:M + 1, 8:N + 8]
+    res_big = torch.full((M + 2, N + 16), 1000.0, device="cuda", dtype=torch.bfloat16)
+    res = res_big[2:, 8:N + 8]
+    res.copy_(torch.randn(M, N, device="cuda"))
+    C.gemm(a, b, out, False, False, res if with_addend else None)
+    _status_ok()
+    ref = a.float() @ b.float().t() + (res.float() if with_addend else 0)
+    assert _close(out, ref)
+    mask = torch.ones_like(big, dtype=torch.bool)
+    mask[1:M + 1, 8:N + 8] = False
+    assert (big[mask] == 7.0).all()
+
+
 def test_gemm_large_persistent(C):
     torch.manual_seed(1)
     M, N, K = 4096, 4096, 1024
