@@ -240,6 +240,9 @@ def run_ours(args):
             _ext.check_status()
         except Exception as e:  # noqa: BLE001
             out["details"][f"ring_degree_{world}_probe_failed"] = f"{type(e).__name__}: {str(e)[:120]}"
+    opt_ms = eng.optimizer_step_ms()
+    if opt_ms is not None:   # the last step's gradient reduction + clip + AdamW + parameter refresh, slowest rank
+        out["details"]["optimizer_step_ms"] = round(max_over_ranks(opt_ms), 2)
     free_b, total_b = torch.cuda.mem_get_info()
     if memory_fallback:
         out["details"]["memory_fallback"] = memory_fallback

@@ -72,6 +72,7 @@ class LlamaEngine:
             self._rings[d] = self._make_ring(d)
         self.ring_degree = cfg.ring_degree
         self.step_index = 0
+        self._opt_events = None
 
     def _make_ring(self, degree: int) -> RingContext:
         cfg, mc = self.cfg, self.model_cfg
@@ -126,9 +127,23 @@ class LlamaEngine:
         loss = torch.zeros((), device=self.ctx.device, dtype=torch.float32)
         for i in range(tokens.shape[0]):
             loss += self.model.forward_backward(tokens[i: i + 1], targets[i: i + 1], loss_weight, ring)
+        timed = tokens.is_cuda
+        if timed:   # two event records per step; read through optimizer_step_ms() once the step has finished
+            if self._opt_events is None:
+                self._opt_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._opt_events[0].record()
         self.optimizer.step(lr=lr)
+        if timed:
+            self._opt_events[1].record()
         self.step_index += 1
         return loss
+
+    def optimizer_step_ms(self) -> Optional[float]:
+        """Device time of the last optimizer step (gradient reduction, clipping, update, parameter refresh; on
+        several ranks it includes waiting for the slowest peer). None before the first GPU step has completed."""
+        if self._opt_events is None or not self._opt_events[1].query():
+            return None
+        return self._opt_events[0].elapsed_time(self._opt_events[1])
 
     def global_loss(self, local_loss: torch.Tensor) -> float:
         t = local_loss.detach().clone()
