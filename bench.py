@@ -39,6 +39,8 @@ def parse_args():
     ap.add_argument("--ring-degree", type=int, default=0, help="context-parallel degree (default: the planner chooses dp x cp)")
     ap.add_argument("--no-fused-peer", action="store_true", help="NCCL reduce-scatter/all-gather optimizer path")
     ap.add_argument("--remat", default="auto", choices=["auto", "full", "selective", "none"])
+    ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"],
+                    help="storage of Adam's moments (auto: the planner takes bf16 only where the memory buys >= 2 %%)")
     ap.add_argument("--ring-probe-steps", type=int, default=0,
                     help="N > 1: also time this many steps with the ring over all N GPUs (secondary key)")
     return ap.parse_args()
@@ -124,11 +126,12 @@ def run_ours(args):
         from zenyx_b200.planner import plan
 
         cp = plan(mc, args.seq_len, args.global_batch, world, hbm_bytes=float(torch.cuda.mem_get_info()[1]),
-                  memory_fraction=0.93).cp
+                  memory_fraction=0.93, optimizer_state_dtype=args.opt_state).cp
     remat = {"auto": None, "full": RematPolicy.full(), "selective": RematPolicy.selective(),
              "none": RematPolicy.none()}[args.remat]
     tcfg = TrainerConfig(lr=3e-4, seq_len=args.seq_len, global_batch=args.global_batch, ring_degree=cp,
-                         weight_decay=0.1, max_grad_norm=1.0, remat=remat, fused_peer=not args.no_fused_peer,
+                         weight_decay=0.1, max_grad_norm=1.0, remat=remat, optimizer_state_dtype=args.opt_state,
+                         fused_peer=not args.no_fused_peer,
                          ring_degrees=(world,) if (args.ring_probe_steps > 0 and world > 1) else ())
     trainer = Trainer(mc, tcfg)
     eng = trainer.engine
@@ -157,17 +160,19 @@ def run_ours(args):
             trainer.train_step(host_tokens[i], host_targets[i])
     except torch.cuda.OutOfMemoryError:
         # The planner sizes the kept activations from the device's total memory; if this box has less of it free
-        # than that (a single GPU is planned to 93 %), fall back once to the policy that recomputes the projections.
+        # than that (a single GPU is planned to 93 %), fall back once to the plain single-GPU configuration: fp32
+        # moments, gate|up recomputed in every layer.
         if world > 1 or args.remat != "auto":
             raise
-        memory_fallback = "selective"
+        memory_fallback = "x,attn,h1,qkv kept, fp32 moments"
         trainer.close()
         del trainer, eng
         import gc
 
         gc.collect()
         torch.cuda.empty_cache()
-        tcfg.remat = RematPolicy.selective()
+        tcfg.remat = RematPolicy(("x", "attn", "h1", "qkv"))
+        tcfg.optimizer_state_dtype = "fp32"
         trainer = Trainer(mc, tcfg)
         eng = trainer.engine
         for i in range(args.warmup):
@@ -207,9 +212,10 @@ def run_ours(args):
         "impl": "zenyx_b200",
         "config": workload_config(args, f"dp{world // cp}" + (f"xcp{cp}" if cp > 1 else ""),
                                   "zenyx_b200 Trainer/LlamaEngine: tcgen05 GEMM + flash-attention kernels, sharded AdamW "
-                                  "with fp32 master and grad clip 1.0, " +
+                                  f"with fp32 master, {eng.optimizer_state_dtype} moments and grad clip 1.0, " +
                                   ("fused P2P reduce-scatter+update+all-gather" if eng.optimizer.fused_peer else "NCCL")),
-        "details": {"remat": list(eng.model.remat.saved), "mfu_of_measured_sustained": None},
+        "details": {"remat": list(eng.model.remat.saved), "remat_gate_up_layers": eng.model.remat.gu_layers,
+                    "optimizer_moments": eng.optimizer_state_dtype, "mfu_of_measured_sustained": None},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
     }
     try:

@@ -466,7 +466,9 @@ void zero_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>
   TORCH_CHECK(grad_ptrs.size() == param_ptrs.size(), "zero_step: peer lists differ");
   TORCH_CHECK(shard_begin % 4 == 0 && n_shard % 4 == 0, "zero_step: shard bounds must be multiples of 4");
   TORCH_CHECK(p_lo.is_cuda() && p_lo.element_size() == 2 && p_lo.numel() >= n_shard && m.numel() >= n_shard &&
-                  v.numel() >= n_shard && m.scalar_type() == torch::kFloat32 && v.scalar_type() == torch::kFloat32,
+                  v.numel() >= n_shard && m.scalar_type() == v.scalar_type() &&
+                  (m.scalar_type() == torch::kFloat32 || m.scalar_type() == torch::kBFloat16) && m.is_contiguous() &&
+                  v.is_contiguous(),
               "zero_step: shard state has the wrong size or type");
   zx::ZeroArgs a;
   a.grads = to_ptrs(grad_ptrs);
@@ -485,8 +487,9 @@ void zero_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>
     TORCH_CHECK(do_reduce && (do_update || !zero_grads), "zero_step: this pass needs a g_shard buffer");
   }
   a.p_lo = reinterpret_cast<int16_t*>(p_lo.data_ptr());
-  a.m = m.data_ptr<float>();
-  a.v = v.data_ptr<float>();
+  a.m = m.data_ptr();
+  a.v = v.data_ptr();
+  a.state_bf16 = m.scalar_type() == torch::kBFloat16 ? 1 : 0;
   a.sumsq = sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr;
   a.clip_coef = clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr;
   a.do_reduce = do_reduce; a.do_update = do_update; a.zero_grads = zero_grads;

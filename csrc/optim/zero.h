@@ -21,8 +21,9 @@ struct ZeroArgs {
   // local shard state
   float* g_shard = nullptr;    // [n_shard] reduced gradient (written in reduce mode, read in update mode)
   int16_t* p_lo = nullptr;     // [n_shard]
-  float* m = nullptr;          // [n_shard]
-  float* v = nullptr;          // [n_shard]
+  void* m = nullptr;           // [n_shard] fp32, or bf16 when state_bf16
+  void* v = nullptr;           // [n_shard]
+  int state_bf16 = 0;          // Adam's moments are stored as bf16 (arithmetic stays fp32; the master weight is unaffected)
   float* sumsq = nullptr;      // [1] accumulates the squared norm of the reduced shard (reduce mode)
   const float* clip_coef = nullptr;  // [1] optional device-side factor applied to the gradient
   int do_reduce = 1;           // sum the shard over all ranks' gradient buffers (P2P loads)

@@ -22,8 +22,8 @@ struct ZParams {
   size_t shard_begin, n_shard, decay_end;
   float* g_shard;
   int16_t* p_lo;
-  float* m;
-  float* v;
+  void* m;
+  void* v;
   float* sumsq;
   const float* clip_coef;
   int do_reduce, do_update, zero_grads;
@@ -45,7 +45,26 @@ struct Group {   // one float4 group of every stream
   uint2 hi, lo;
 };
 
-template <int NR>
+// Adam's moments in memory: fp32, or bf16 (SB) to halve their footprint; the arithmetic is fp32 either way.
+template <bool SB>
+__device__ __forceinline__ float4 ld_state(const void* base, size_t i) {
+  if constexpr (SB) {
+    const uint2 u = reinterpret_cast<const uint2*>(base)[i];
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+  } else {
+    return reinterpret_cast<const float4*>(base)[i];
+  }
+}
+template <bool SB>
+__device__ __forceinline__ void st_state(void* base, size_t i, const float* x) {
+  if constexpr (SB)
+    reinterpret_cast<uint2*>(base)[i] = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+  else
+    reinterpret_cast<float4*>(base)[i] = make_float4(x[0], x[1], x[2], x[3]);
+}
+
+template <int NR, bool SB>
 __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
   __shared__ float s_red[8];
   const size_t nvec = p.n_shard >> 2;
@@ -91,8 +110,8 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
       if (p.do_update) {
         u[q].hi = *reinterpret_cast<const uint2*>(own_params + gi);
         u[q].lo = reinterpret_cast<const uint2*>(p.p_lo)[i];
-        u[q].mm = reinterpret_cast<const float4*>(p.m)[i];
-        u[q].vv = reinterpret_cast<const float4*>(p.v)[i];
+        u[q].mm = ld_state<SB>(p.m, i);
+        u[q].vv = ld_state<SB>(p.v, i);
       }
     }
     // ---- arithmetic and stores ----
@@ -137,8 +156,8 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZParams p) {
         nh[j] = hh & 0xffffu;
         nl[j] = (bits - (hh << 16)) & 0xffffu;
       }
-      reinterpret_cast<float4*>(p.m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
-      reinterpret_cast<float4*>(p.v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+      st_state<SB>(p.m, i, ma);
+      st_state<SB>(p.v, i, va);
       reinterpret_cast<uint2*>(p.p_lo)[i] = make_uint2(nl[0] | (nl[1] << 16), nl[2] | (nl[3] << 16));
       const uint2 new_hi = make_uint2(nh[0] | (nh[1] << 16), nh[2] | (nh[3] << 16));
       // all-gather: push the new bf16 parameters into every rank's buffer
@@ -178,13 +197,20 @@ void launch_zero_step(const ZeroArgs& a) {
   size_t blocks = (nvec + 256 * ZERO_UNROLL - 1) / (256 * ZERO_UNROLL);
   const size_t cap = (size_t)a.sm_count * 64;   // several waves: the tail of one hides under the head of the next
   if (blocks > cap) blocks = cap;
+  const unsigned nb = (unsigned)blocks;
+#define ZX_ZERO_LAUNCH(NR)                                                            \
+  do {                                                                                \
+    if (a.state_bf16) zero_step_kernel<NR, true><<<nb, 256, 0, a.stream>>>(p);        \
+    else zero_step_kernel<NR, false><<<nb, 256, 0, a.stream>>>(p);                    \
+  } while (0)
   switch (a.nranks) {
-    case 1: zero_step_kernel<1><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
-    case 2: zero_step_kernel<2><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
-    case 4: zero_step_kernel<4><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
-    case 8: zero_step_kernel<8><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
-    default: zero_step_kernel<0><<<(unsigned)blocks, 256, 0, a.stream>>>(p); break;
+    case 1: ZX_ZERO_LAUNCH(1); break;
+    case 2: ZX_ZERO_LAUNCH(2); break;
+    case 4: ZX_ZERO_LAUNCH(4); break;
+    case 8: ZX_ZERO_LAUNCH(8); break;
+    default: ZX_ZERO_LAUNCH(0); break;
   }
+#undef ZX_ZERO_LAUNCH
 }
 
 }  // namespace zx

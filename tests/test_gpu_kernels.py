@@ -362,6 +362,37 @@ def test_adamw_split_master(C):
     assert abs(ss.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
 
 
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+def test_zero_step_kernel_matches_the_host_path(C, state_dtype):
+    """The fused optimizer kernel (norm pass, clip, AdamW on the split master, parameter refresh) against the same
+    optimizer on CPU tensors, for fp32 and for bf16 moments."""
+    from zenyx_b200.models.llama import FlatBuffers
+    from zenyx_b200.parallel.zero import ZeroAdamW
+
+    specs = [("w", (256, 384), True), ("n", (256,), False)]
+    torch.manual_seed(21)
+    gpu = FlatBuffers(specs, "cuda")
+    cpu = FlatBuffers(specs, "cpu")
+    init = (torch.randn(gpu.total) * 0.1).bfloat16()
+    gpu.params.copy_(init)
+    cpu.params.copy_(init)
+    kw = dict(lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, single_process=True, state_dtype=state_dtype)
+    og, oc = ZeroAdamW(gpu, **kw), ZeroAdamW(cpu, **kw)
+    assert og.fused_peer and og.m.dtype == state_dtype
+    for _ in range(6):
+        g = torch.randn(gpu.total) * 0.5
+        gpu.grads.copy_(g)
+        cpu.grads.copy_(g)
+        og.step()
+        oc.step()
+    _status_ok()
+    assert float(gpu.grads.abs().sum()) == 0.0                      # consumed and cleared
+    assert _rel_err(gpu.params.float().cpu(), cpu.params.float()) < 4e-3
+    assert _rel_err(og.m.float().cpu(), oc.m.float()) < (1e-5 if state_dtype == torch.float32 else 6e-3)
+    assert _rel_err(og.v.float().cpu(), oc.v.float()) < (1e-5 if state_dtype == torch.float32 else 6e-3)
+    assert abs(og.grad_norm.item() - oc.grad_norm.item()) / oc.grad_norm.item() < 1e-4
+
+
 def _attn_bwd_ref(q, k, v, do, scale, qpos, kpos, causal, wb=0, ge=0):
     qf = q.float().requires_grad_(True)
     kf = k.float().requires_grad_(True)

@@ -15,13 +15,15 @@ def _models(policy):
     return cfg, gpu, cpu
 
 
-@pytest.mark.parametrize("policy_name", ["selective", "none", "full", "host_offload"])
+@pytest.mark.parametrize("policy_name", ["selective", "none", "full", "host_offload", "gate_up_in_first_layer"])
 def test_llama_gpu_matches_cpu_fp32(policy_name):
     from zenyx_b200.models import RematPolicy
     from zenyx_b200.ops import _ext
 
     torch.manual_seed(0)
-    cfg, gpu, cpu = _models(getattr(RematPolicy, policy_name)())
+    policy = (RematPolicy(("x", "attn", "h1", "qkv", "gu"), gu_layers=1) if policy_name == "gate_up_in_first_layer"
+              else getattr(RematPolicy, policy_name)())
+    cfg, gpu, cpu = _models(policy)
     tokens = torch.randint(0, cfg.vocab_size, (2, 512))
     targets = torch.randint(0, cfg.vocab_size, (2, 512))
     l_cpu = cpu.forward_backward(tokens, targets)

@@ -80,6 +80,11 @@ def test_llama_manual_backward_full_and_none():
     _check(RematPolicy.none())
 
 
+def test_llama_manual_backward_gate_up_kept_in_some_layers():
+    _check(RematPolicy(("x", "attn", "h1", "qkv", "gu"), gu_layers=1))
+    _check(RematPolicy(("x", "attn", "gu"), gu_layers=0))
+
+
 def test_llama_autograd_loss_entry_point():
     torch.manual_seed(1)
     cfg = LlamaConfig.tiny(n_layers=1, d_model=64, n_heads=2, n_kv_heads=2, ffn_dim=96, vocab_size=128)

@@ -177,19 +177,59 @@ def test_planner_choices_for_the_8b_configuration():
     assert free.dp * free.cp == 8
     # sized for the real device (192 GB) the planner splits 1 / 2 / 4 / 8 GPUs the way the runs were measured:
     # ring steps are charged, so a ring is only as long as memory requires
-    layouts = {n: plan(cfg, 32768, 8, n, hbm_bytes=192.26e9, memory_fraction=0.93) for n in (1, 2, 4, 8)}
+    layouts = {n: plan(cfg, 32768, 8, n, hbm_bytes=192.26e9, memory_fraction=0.93, optimizer_state_dtype="fp32")
+               for n in (1, 2, 4, 8)}
     assert [(layouts[n].dp, layouts[n].cp) for n in (1, 2, 4, 8)] == [(1, 1), (1, 2), (2, 2), (8, 1)]
     assert set(layouts[1].remat.saved) == {"x", "attn", "h1", "qkv"}
     assert all(set(layouts[n].remat.saved) == set(RematPolicy.none().saved) for n in (2, 4, 8))
+    assert all(layouts[n].optimizer_state_dtype == "fp32" and layouts[n].remat.gu_layers == -1 for n in (1, 2, 4, 8))
+    # left to itself the planner takes bf16 moments only where the memory buys step time: on one GPU (32 GB = the
+    # gate|up projection of 17 more layers), not where everything is kept anyway
+    auto = {n: plan(cfg, 32768, 8, n, hbm_bytes=192.26e9, memory_fraction=0.93) for n in (1, 2, 8)}
+    assert auto[1].optimizer_state_dtype == "bf16" and "gu" in auto[1].remat.saved and 12 <= auto[1].remat.gu_layers <= 20
+    assert auto[1].estimate.total_bytes <= 0.93 * 192.26e9
+    assert auto[1].estimate.step_s < 0.97 * layouts[1].estimate.step_s
+    assert all(auto[n].optimizer_state_dtype == "fp32" and auto[n].remat.gu_layers == -1 for n in (2, 8))
+    assert "bf16 moments" in auto[1].describe() and "17 layers" in auto[1].describe()
     from zenyx_b200.planner.cost_model import estimate
     e1, e8 = (estimate(cfg, 32768, 8, 8, cp, RematPolicy.none()) for cp in (1, 8))
     assert 1.15 < e8.step_s / e1.step_s < 1.3          # measured 3.68 s vs 3.06 s per step
     # host offload is an explicit policy, never the planner's choice, however much host memory there is
     assert all("gu@host" not in plan(cfg, 32768, 8, n, hbm_bytes=192.26e9, memory_fraction=0.95,
                                      host_bytes=4e12).remat.saved for n in (1, 2))
+    part = RematPolicy(("x", "attn", "gu"), gu_layers=8)
+    assert part.keeps_gu(7) and not part.keeps_gu(8) and part.gu_fraction(cfg) == 0.25
+    assert part.bytes_per_token_per_layer(cfg) == RematPolicy.selective().bytes_per_token_per_layer(cfg) + cfg.ffn_dim
     assert RematPolicy.host_offload().host_bytes_per_token_per_layer(cfg) == 4 * cfg.ffn_dim
     with pytest.raises(ValueError):
         plan(cfg, 1 << 20, 8, 1, hbm_bytes=40e9)
+
+
+def test_adamw_with_bf16_moments_tracks_the_fp32_state():
+    """Moments stored as bf16 (arithmetic and master weight in fp32): after some steps on the same gradients the
+    parameters stay within bf16 resolution of the run with fp32 moments, and the state really is half the size."""
+    from zenyx_b200.models.llama import FlatBuffers
+    from zenyx_b200.parallel.zero import ZeroAdamW
+
+    specs = [("w", (64, 96), True), ("n", (64,), False)]
+    runs = {}
+    for dt in (torch.float32, torch.bfloat16):
+        torch.manual_seed(11)
+        flat = FlatBuffers(specs, "cpu")
+        flat.params.copy_(torch.randn(flat.total) * 0.1)
+        opt = ZeroAdamW(flat, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, single_process=True, state_dtype=dt)
+        for _ in range(12):
+            flat.grads.copy_(torch.randn(flat.total) * 0.5)
+            opt.step()
+        assert opt.m.dtype == dt and opt.v.dtype == dt
+        runs[dt] = (flat.params.float().clone(), opt.m.float().clone(), opt.v.float().clone())
+    p32, m32, v32 = runs[torch.float32]
+    p16, m16, v16 = runs[torch.bfloat16]
+    assert ((p16 - p32).norm() / p32.norm()).item() < 2e-2
+    assert ((m16 - m32).norm() / m32.norm()).item() < 1e-2 and ((v16 - v32).norm() / v32.norm()).item() < 1e-2
+    assert not torch.equal(p16, p32)   # it is a different storage format, not an alias of the fp32 path
+    with pytest.raises(AssertionError):
+        ZeroAdamW(FlatBuffers(specs, "cpu"), state_dtype=torch.float16)
 
 
 def test_checkpoint_roundtrip_and_resume_is_bit_exact(tmp_path):

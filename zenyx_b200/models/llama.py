@@ -88,6 +88,10 @@ class RematPolicy:
     """
 
     saved: Tuple[str, ...] = ("x", "attn")
+    # With "gu" in ``saved``: keep the gate|up projection (the largest activation, 4 * ffn_dim bytes per token)
+    # only in the first ``gu_layers`` layers and recompute it in the others; -1 = in every layer. Lets the
+    # planner spend whatever memory is left after the cheaper activations instead of all or nothing.
+    gu_layers: int = -1
 
     @classmethod
     def full(cls) -> "RematPolicy":        # recompute everything, attention included
@@ -108,10 +112,20 @@ class RematPolicy:
     def host_bytes_per_token_per_layer(self, cfg: LlamaConfig) -> int:
         return 2 * 2 * cfg.ffn_dim if "gu@host" in self.saved else 0
 
-    def bytes_per_token_per_layer(self, cfg: LlamaConfig) -> int:
+    def keeps_gu(self, layer: int) -> bool:
+        return "gu" in self.saved and (self.gu_layers < 0 or layer < self.gu_layers)
+
+    def gu_fraction(self, cfg: LlamaConfig) -> float:
+        """Share of the layers whose gate|up projection is kept."""
+        if "gu" not in self.saved:
+            return 0.0
+        return 1.0 if self.gu_layers < 0 else min(self.gu_layers, cfg.n_layers) / max(1, cfg.n_layers)
+
+    def bytes_per_token_per_layer(self, cfg: LlamaConfig) -> float:
+        """Average over the layers (the gate|up projection may be kept in some of them only)."""
         sizes = {"x": cfg.d_model, "attn": cfg.n_heads * cfg.head_dim + 2 * cfg.n_heads, "qkv": cfg.qkv_dim,
-                 "h1": cfg.d_model, "gu": 2 * cfg.ffn_dim, "gu@host": 0}
-        return 2 * sum(sizes[n] for n in self.saved)
+                 "h1": cfg.d_model, "gu": 0, "gu@host": 0}
+        return 2 * sum(sizes[n] for n in self.saved) + 2 * 2 * cfg.ffn_dim * self.gu_fraction(cfg)
 
 
 class FlatBuffers:
@@ -328,7 +342,7 @@ class LlamaModel(nn.Module):
                     saved["k"], saved["v"] = k.clone(), v.clone()
             if "h1" in names:
                 saved["h1"] = h1
-            if "gu" in names:
+            if self.remat.keeps_gu(l):
                 saved["gu"] = gu
             elif "gu@host" in names and gu.is_cuda:
                 self._offload_gu(l, gu)

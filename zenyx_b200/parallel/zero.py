@@ -26,7 +26,14 @@ from ..ops import _ext, fused
 class ZeroAdamW:
     def __init__(self, flat, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1,
                  max_grad_norm: Optional[float] = None, group=None, fused_peer: bool = True,
-                 barrier_timeout_ms: float = 60000.0, single_process: bool = False):
+                 barrier_timeout_ms: float = 60000.0, single_process: bool = False,
+                 state_dtype: torch.dtype = torch.float32):
+        """``state_dtype``: storage type of Adam's two moments, fp32 or bf16. bf16 halves their 8 bytes per
+        parameter (32 GB for an 8B model on one GPU, which the planner spends on kept activations); the update
+        arithmetic and the master weight stay fp32. The reference keeps parameters and both moments in bf16
+        with no master copy at all (torch.optim.AdamW on a bf16 model, zenyx/train/trainer.py:29)."""
+        assert state_dtype in (torch.float32, torch.bfloat16), "optimizer moments are kept in fp32 or bf16"
+        self.state_dtype = state_dtype
         self.flat = flat
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
@@ -40,8 +47,8 @@ class ZeroAdamW:
         dev = flat.params.device
         self.device = dev
         self.p_lo = torch.zeros(self.n_shard, device=dev, dtype=torch.int16)
-        self.m = torch.zeros(self.n_shard, device=dev, dtype=torch.float32)
-        self.v = torch.zeros(self.n_shard, device=dev, dtype=torch.float32)
+        self.m = torch.zeros(self.n_shard, device=dev, dtype=state_dtype)
+        self.v = torch.zeros(self.n_shard, device=dev, dtype=state_dtype)
         self.step_count = 0
         self.on_gpu = dev.type == "cuda"
         self.fused_peer = fused_peer and self.on_gpu and (self.world == 1 or flat.sym_grads is not None)
@@ -127,11 +134,17 @@ class ZeroAdamW:
             coef = self.clip
         lo, hi, mid = self._local_slices()
         p_shard = self.flat.params[lo:hi]
+        # this path's update routine works on fp32 moments: widen bf16 ones for the call and round them back
+        narrow = self.state_dtype != torch.float32
+        m32, v32 = (self.m.float(), self.v.float()) if narrow else (self.m, self.v)
         for a, b, wd in ((0, mid - lo, self.weight_decay), (mid - lo, hi - lo, 0.0)):
             if b > a:
-                fused.adamw_step_(p_shard[a:b], self.p_lo[a:b], self.m[a:b], self.v[a:b], self.g_shard[a:b], lr=lr,
+                fused.adamw_step_(p_shard[a:b], self.p_lo[a:b], m32[a:b], v32[a:b], self.g_shard[a:b], lr=lr,
                                   beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd, step=self.step_count,
                                   grad_scale=grad_scale, grad_scale_tensor=coef)
+        if narrow:
+            self.m.copy_(m32)
+            self.v.copy_(v32)
         if self.world > 1:
             dist.all_gather_into_tensor(self.flat.params, p_shard.clone(), group=self.group)
         grads.zero_()

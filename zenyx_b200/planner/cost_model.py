@@ -48,14 +48,16 @@ class StepEstimate:
 
 
 def estimate(cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, cp: int, remat: RematPolicy,
-             peaks: Optional[HardwarePeaks] = None, zero_shard: bool = True, kernel_efficiency: float = 0.6) -> StepEstimate:
+             peaks: Optional[HardwarePeaks] = None, zero_shard: bool = True, kernel_efficiency: float = 0.6,
+             moment_bytes: int = 4) -> StepEstimate:
+    """``moment_bytes``: storage size of each of Adam's two moments (4 = fp32, 2 = bf16)."""
     peaks = peaks or HardwarePeaks.load()
     P = cfg.num_params()
     dp = n_gpus // cp
     tokens_rank = seq_len // cp                      # one sequence per micro-batch
     micro_batches = max(1, global_batch // dp)
     # parameters bf16 + fp32 gradient buffer are replicated; master remainder + m + v are sharded
-    state = P * (2 + 4) + P * (2 + 4 + 4) / (n_gpus if zero_shard else 1)
+    state = P * (2 + 4) + P * (2 + 2 * moment_bytes) / (n_gpus if zero_shard else 1)
     if n_gpus > 1:
         state += P * 4 / n_gpus   # the reduced fp32 gradient shard kept between the norm pass and the update
     act = remat.bytes_per_token_per_layer(cfg) * tokens_rank * cfg.n_layers
@@ -71,8 +73,8 @@ def estimate(cfg: LlamaConfig, seq_len: int, global_batch: int, n_gpus: int, cp:
         recompute += 2.0 * cfg.qkv_dim * cfg.d_model
     if "h1" not in remat.saved:
         recompute += 2.0 * cfg.n_heads * cfg.head_dim * cfg.d_model
-    if "gu" not in remat.saved and "gu@host" not in remat.saved:
-        recompute += 2.0 * 2 * cfg.ffn_dim * cfg.d_model
+    if "gu@host" not in remat.saved:   # the gate|up projection is recomputed in the layers that do not keep it
+        recompute += 2.0 * 2 * cfg.ffn_dim * cfg.d_model * (1.0 - remat.gu_fraction(cfg))
     if "attn" not in remat.saved:
         recompute += 4.0 * seq_len * cfg.head_dim * cfg.n_heads * 0.5
     del per_layer_mm

@@ -35,6 +35,7 @@ class EngineConfig:
     weight_decay: float = 0.1
     max_grad_norm: Optional[float] = 1.0
     remat: Optional[RematPolicy] = None    # None: ask the planner
+    optimizer_state_dtype: str = "auto"    # "fp32" | "bf16" | "auto" (planner; fp32 when remat is given explicitly)
     fused_peer: bool = True                # False: NCCL reduce-scatter / all-gather baseline path
     layout: str = "zigzag"
     mask: MaskSpec = field(default_factory=MaskSpec)
@@ -50,6 +51,9 @@ class LlamaEngine:
         degrees = sorted(set(list(cfg.ring_degrees) + [cfg.ring_degree]))
         self.mesh = Mesh(degrees, world=world, rank=rank)
         remat = cfg.remat
+        state_dtype = cfg.optimizer_state_dtype
+        if state_dtype not in ("auto", "fp32", "bf16"):
+            raise ValueError("optimizer_state_dtype is 'auto', 'fp32' or 'bf16'")
         if remat is None:
             from ..planner import plan
 
@@ -58,7 +62,12 @@ class LlamaEngine:
                 import torch
 
                 kw = {"hbm_bytes": float(torch.cuda.mem_get_info(self.ctx.device)[1]), "memory_fraction": 0.93}
-            remat = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=max(degrees), **kw).remat
+            chosen = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=max(degrees),
+                          optimizer_state_dtype=state_dtype, **kw)
+            remat, state_dtype = chosen.remat, chosen.optimizer_state_dtype
+        elif state_dtype == "auto":
+            state_dtype = "fp32"
+        self.optimizer_state_dtype = state_dtype
         dev = self.ctx.device
         sym_group = dist.group.WORLD if (world > 1 and dev.type == "cuda" and cfg.fused_peer) else None
         self.model = LlamaModel(model_cfg, device=dev, remat=remat, seed=cfg.seed, symmetric_group=sym_group,
@@ -66,7 +75,8 @@ class LlamaEngine:
         self.optimizer = ZeroAdamW(self.model.flat, lr=cfg.lr, betas=cfg.betas, eps=cfg.eps,
                                    weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
                                    group=dist.group.WORLD if world > 1 else None, fused_peer=cfg.fused_peer,
-                                   barrier_timeout_ms=cfg.barrier_timeout_ms)
+                                   barrier_timeout_ms=cfg.barrier_timeout_ms,
+                                   state_dtype=torch.bfloat16 if state_dtype == "bf16" else torch.float32)
         self._rings: Dict[int, RingContext] = {}
         for d in degrees:
             self._rings[d] = self._make_ring(d)
