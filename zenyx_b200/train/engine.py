@@ -59,8 +59,6 @@ class LlamaEngine:
 
             kw = {}
             if self.ctx.device.type == "cuda":   # size the plan for the memory this GPU really has
-                import torch
-
                 kw = {"hbm_bytes": float(torch.cuda.mem_get_info(self.ctx.device)[1]), "memory_fraction": 0.93}
             chosen = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=max(degrees),
                           optimizer_state_dtype=state_dtype, **kw)
