@@ -77,9 +77,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
-#ifdef ZX_ARRIVE_SYNC
-  __syncwarp();
-#endif
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
@@ -111,9 +108,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 #pragma unroll 1
   for (int i = 0; i < 1024; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef ZX_WAIT_SLEEP
-    __nanosleep(ZX_WAIT_SLEEP);
-#endif
   }
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
