@@ -41,9 +41,13 @@ def parse_args():
     ap.add_argument("--remat", default="auto", choices=["auto", "full", "selective", "none"])
     ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"],
                     help="storage of Adam's moments (auto: the planner takes bf16 only where the memory buys >= 2 %%)")
-    ap.add_argument("--ring-probe-steps", type=int, default=0,
-                    help="N > 1: also time this many steps with the ring over all N GPUs (secondary key)")
-    return ap.parse_args()
+    ap.add_argument("--ring-probe-steps", type=int, default=-1,
+                    help="N > 1: after the timed region, also run this many steps with the ring over all N GPUs and "
+                         "report them as a secondary key (first one untimed; default: 3 when N > 1, 0 disables)")
+    args = ap.parse_args()
+    if args.ring_probe_steps < 0:
+        args.ring_probe_steps = 3 if args.gpus > 1 else 0
+    return args
 
 
 class ClockSampler:

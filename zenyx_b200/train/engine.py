@@ -60,7 +60,8 @@ class LlamaEngine:
             kw = {}
             if self.ctx.device.type == "cuda":   # size the plan for the memory this GPU really has
                 kw = {"hbm_bytes": float(torch.cuda.mem_get_info(self.ctx.device)[1]), "memory_fraction": 0.93}
-            chosen = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=max(degrees),
+            # sized for the shortest ring among the prepared degrees: it holds the most tokens per rank
+            chosen = plan(model_cfg, cfg.seq_len, cfg.global_batch, world, ring_degree=min(degrees),
                           optimizer_state_dtype=state_dtype, **kw)
             remat, state_dtype = chosen.remat, chosen.optimizer_state_dtype
         elif state_dtype == "auto":
