@@ -41,3 +41,20 @@ def test_manager_serves_the_planned_accesses_from_all_tiers(tmp_path, with_file)
     if with_file:
         assert st.bytes_nvme_write > 0 and st.bytes_nvme_read > 0
     mgr.close()
+
+
+def test_ring_attention_over_tiered_kv_single_rank(capsys):
+    """The tiered ring benchmark at ring degree 1 on a small case: every layer's K/V goes through the manager
+    under a budget smaller than one layer, the attention kernels run on what it hands out, the step reports
+    spills and a finite time."""
+    import json
+
+    from zenyx_b200.bench import ring_tiering
+
+    ring_tiering.main(["--seq-len", "8192", "--layers", "3", "--block-tokens", "1024", "--hbm-gb", "0.004",
+                       "--steps", "2"])
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["ring_degree"] == 1 and rec["layers"] == 3 and rec["value"] > 0
+    assert rec["share_kv_bytes"] > rec["hbm_budget_bytes"]
+    assert rec["measured"]["misses"] > 0 and rec["measured"]["bytes_h2d"] > 0
+    assert rec["measured"]["peak_hbm_bytes"] <= rec["hbm_budget_bytes"]
