@@ -181,3 +181,21 @@ def test_streamer_binds_weights_and_engine_runs():
     eng.kv_manager.put("b0", torch.randn(4))
     loss = eng.run_forward_backward(torch.randn(2, 8), torch.randn(2, 4), nn.MSELoss())
     assert loss >= 0 and model[0].weight.grad is not None and len(eng.last_samples) == 3
+
+
+def test_tiered_ring_benchmark_follows_the_managers_plan():
+    """The acquires that bench/ring_tiering.py makes per step are exactly the manager's planned accesses of the
+    rank, in order, for every rank of a ring: the manager then evicts and prefetches by its Belady plan instead of
+    falling back to out-of-plan handling."""
+    from zenyx_b200.bench.ring_tiering import acquire_order
+    from zenyx_b200.train.belayd_kv_cache_tiering import BeladyKVCacheTieringManager
+
+    for ring, layers, nb in ((1, 3, 4), (2, 4, 8), (4, 2, 4), (8, 3, 2)):
+        bt = 256
+        for rank in range(ring):
+            mgr = BeladyKVCacheTieringManager(num_devices=ring, context_length=ring * nb * bt, num_layers=layers,
+                                              num_kv_heads=2, head_dim=64, tier_block_tokens=bt,
+                                              hbm_budget_bytes=3 * 2 * bt * 2 * 64 * 2, simulate=True, rank=rank)
+            assert mgr.blocks_per_layer == nb
+            ids = [layer * nb + b for layer, b in acquire_order(ring, layers, nb)]
+            assert ids == list(mgr.plan().ids), (ring, layers, nb, rank)

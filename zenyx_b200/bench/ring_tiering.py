@@ -28,6 +28,18 @@ import torch
 import torch.distributed as dist
 
 
+def acquire_order(ring_degree: int, layers: int, blocks_per_layer: int):
+    """(layer, block) of every ``acquire`` one step of this benchmark makes, in order: forward over the layers, then
+    backward in reverse; per layer the rank's own pass over its blocks followed by one pass per peer. This is the
+    order of ``RingAttentionAccessSequence.block_ids(rank)``, which is what keeps the manager on its plan."""
+    out = []
+    for order in (range(layers), reversed(range(layers))):
+        for layer in order:
+            for _ in range(ring_degree):
+                out.extend((layer, b) for b in range(blocks_per_layer))
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--seq-len", type=int, default=1 << 20)
