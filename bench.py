@@ -231,9 +231,25 @@ def run_ours(args):
         out["details"]["peaks"] = pk.source
     except Exception:  # noqa: BLE001
         pass
+    opt_ms = eng.optimizer_step_ms()
+    if opt_ms is not None:   # the last timed step's gradient reduction + clip + AdamW + parameter refresh, slowest rank
+        out["details"]["optimizer_step_ms"] = round(max_over_ranks(opt_ms), 2)
+    out["details"]["peak_torch_alloc_gb"] = round(torch.cuda.max_memory_allocated() / 1e9, 1)
+    if memory_fallback:
+        out["details"]["memory_fallback"] = memory_fallback
     if args.ring_probe_steps > 0 and world > 1 and cp != world:
-        # secondary figure: the same step with the context-parallel ring over all GPUs (first probe step untimed);
-        # a failure here must not cost the main result
+        # secondary figure: the same step with the context-parallel ring over all GPUs (first probe step untimed).
+        # A failure here must not cost the main result: exceptions are recorded, and if the probe does not come
+        # back within its time limit every rank leaves through the watchdog, rank 0 printing the line first.
+        def bail():
+            out["details"][f"ring_degree_{world}_probe_failed"] = "no result within 180 s"
+            if rank == 0:
+                print(json.dumps(out), flush=True)
+            os._exit(0)
+
+        watchdog = threading.Timer(180.0, bail)
+        watchdog.daemon = True
+        watchdog.start()
         try:
             eng.set_ring_degree(world)
             pbase = args.warmup + args.steps
@@ -250,13 +266,8 @@ def run_ours(args):
             _ext.check_status()
         except Exception as e:  # noqa: BLE001
             out["details"][f"ring_degree_{world}_probe_failed"] = f"{type(e).__name__}: {str(e)[:120]}"
-    opt_ms = eng.optimizer_step_ms()
-    if opt_ms is not None:   # the last step's gradient reduction + clip + AdamW + parameter refresh, slowest rank
-        out["details"]["optimizer_step_ms"] = round(max_over_ranks(opt_ms), 2)
+        watchdog.cancel()
     free_b, total_b = torch.cuda.mem_get_info()
-    if memory_fallback:
-        out["details"]["memory_fallback"] = memory_fallback
-    out["details"]["peak_torch_alloc_gb"] = round(torch.cuda.max_memory_allocated() / 1e9, 1)
     out["details"]["device_mem_used_gb"] = round((total_b - free_b) / 1e9, 1)   # includes peer buffers and the context
     if rank == 0:
         print(json.dumps(out), flush=True)
