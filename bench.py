@@ -235,6 +235,8 @@ def run_ours(args):
     if opt_ms is not None:   # the last timed step's gradient reduction + clip + AdamW + parameter refresh, slowest rank
         out["details"]["optimizer_step_ms"] = round(max_over_ranks(opt_ms), 2)
     out["details"]["peak_torch_alloc_gb"] = round(torch.cuda.max_memory_allocated() / 1e9, 1)
+    free_b, total_b = torch.cuda.mem_get_info()
+    out["details"]["device_mem_used_gb"] = round((total_b - free_b) / 1e9, 1)   # includes peer buffers and the context
     if memory_fallback:
         out["details"]["memory_fallback"] = memory_fallback
     if args.ring_probe_steps > 0 and world > 1 and cp != world:
@@ -267,13 +269,19 @@ def run_ours(args):
         except Exception as e:  # noqa: BLE001
             out["details"][f"ring_degree_{world}_probe_failed"] = f"{type(e).__name__}: {str(e)[:120]}"
         watchdog.cancel()
-    free_b, total_b = torch.cuda.mem_get_info()
-    out["details"]["device_mem_used_gb"] = round((total_b - free_b) / 1e9, 1)   # includes peer buffers and the context
     if rank == 0:
         print(json.dumps(out), flush=True)
-    trainer.close()
-    if world > 1:
-        dist.destroy_process_group()
+    # the line is out; nothing in the teardown may turn the run into a failure or keep it from ending
+    closer = threading.Timer(120.0, lambda: os._exit(0))
+    closer.daemon = True
+    closer.start()
+    try:
+        trainer.close()
+        if world > 1:
+            dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        print(f"teardown: {type(e).__name__}: {e}", file=sys.stderr)
+    closer.cancel()
 
 
 def main():
